@@ -110,6 +110,11 @@ class GroupGeometry:
     cap: int
     n_pages: int
     entries: List[int] = field(default_factory=list)     # cache entry ids, in order
+    value_dim: int = 0                                   # 0: values as wide as keys
+
+    @property
+    def v_dim(self) -> int:
+        return self.value_dim or self.head_dim
 
     @property
     def max_pages(self) -> int:
@@ -209,12 +214,16 @@ def plan_groups(requests: Sequence[object], max_tokens: int, max_seq_len: int,
         if not isinstance(r, KVRequest):
             continue
         window = r.window if (r.window is not None and round_up(r.window, PAGE) < full_cap) else None
-        key = (r.n_kv_heads, r.head_dim, window)
+        value_dim = getattr(r, "value_dim", 0)
+        if value_dim == r.head_dim:
+            value_dim = 0
+        key = (r.n_kv_heads, r.head_dim, window, value_dim)
         if key not in index:
             cap = full_cap if window is None else round_up(window, PAGE)
             n_pages = min(budget_pages, n_slots * (cap // PAGE))
             index[key] = len(groups)
-            groups.append(GroupGeometry(r.n_kv_heads, r.head_dim, window, cap, max(1, n_pages)))
+            groups.append(GroupGeometry(r.n_kv_heads, r.head_dim, window, cap, max(1, n_pages),
+                                        value_dim=value_dim))
         g = index[key]
         where[entry] = (g, len(groups[g].entries))
         groups[g].entries.append(entry)

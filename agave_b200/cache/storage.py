@@ -1,7 +1,8 @@
 """The cache on the device: page pools per group, page tables, fixed-size state.
 
 Layout of one group: keys and values ``[entries, pages, PAGE, n_kv_heads,
-head_dim]`` in the compute dtype, and one page table ``[slots, max_pages]``
+head_dim]`` in the compute dtype (the values ``[..., value_dim]`` where a group's
+value heads have a size of their own), and one page table ``[slots, max_pages]``
 (int32) shared by the group's entries.  Position p of the sequence in slot s is
 row p % cap; its page is ``page_table[s, row // PAGE]``.  Nothing is cleared
 when a slot is reused: every read is bounded by the sequence's length.
@@ -51,9 +52,9 @@ class Cache:
         self.v_pools: List[torch.Tensor] = []
         self.tables: List[torch.Tensor] = []
         for g in groups:
-            shape = (len(g.entries), g.n_pages, PAGE, g.n_kv_heads, g.head_dim)
-            self.k_pools.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v_pools.append(torch.zeros(shape, dtype=dtype, device=device))
+            shape = (len(g.entries), g.n_pages, PAGE, g.n_kv_heads)
+            self.k_pools.append(torch.zeros(shape + (g.head_dim,), dtype=dtype, device=device))
+            self.v_pools.append(torch.zeros(shape + (g.v_dim,), dtype=dtype, device=device))
             self.tables.append(torch.zeros((n_slots, g.max_pages), dtype=torch.int32,
                                            device=device))
         # fixed-size state: one tensor per distinct size

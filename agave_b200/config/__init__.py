@@ -1,12 +1,15 @@
 from .base import (AttentionSpec, BlockSpec, ConfigError, GatedFeedForwardSpec, LayerCall,
-                   ModelSpec, NormSpec, RotarySpec, default_schedule)
+                   LayerNormSpec, ModelSpec, NormSpec, QueryTemperatureSpec,
+                   RoutedFeedForwardSpec, RotarySpec, default_schedule)
 from .registry import (load_config, read_config_json, register_architecture,
                        registered_architectures, resolve_architecture)
 from .gemma3 import Gemma3Config
+from .ramilorn import RamilornConfig
 
 __all__ = [
     "AttentionSpec", "BlockSpec", "ConfigError", "GatedFeedForwardSpec", "LayerCall",
-    "ModelSpec", "NormSpec", "RotarySpec", "default_schedule", "load_config",
+    "LayerNormSpec", "ModelSpec", "NormSpec", "QueryTemperatureSpec", "RoutedFeedForwardSpec",
+    "RotarySpec", "RamilornConfig", "default_schedule", "load_config",
     "read_config_json", "register_architecture", "registered_architectures",
     "resolve_architecture", "Gemma3Config",
 ]

@@ -47,6 +47,23 @@ class NormSpec:
 
 
 @dataclass(frozen=True)
+class LayerNormSpec:
+    """Layer norm with weight and bias: (x - mean) / sqrt(var + eps) * w + b, the variance
+    being the mean of the squared deviations; ``bias`` False leaves b out."""
+    kind: str = "layernorm"
+    eps: float = 1e-5
+    bias: bool = True
+
+
+@dataclass(frozen=True)
+class QueryTemperatureSpec:
+    """The queries at position p are multiplied by 1 + coef * ln(floor((p + 1) / every) + 1):
+    attention sharpens in steps as the context grows."""
+    coef: float = 0.0
+    every: int = 1
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
     """Grouped-query softmax attention over a key/value cache.
 
@@ -62,6 +79,19 @@ class AttentionSpec:
     window: Optional[int] = None
     qk_norm: Optional[NormSpec] = None      # per-head norm of q and k, before the rotation
     position: Optional[RotarySpec] = None
+    # the size of a value head where it differs from head_dim (0: the same)
+    value_dim: int = 0
+    # a learned logit per query head that joins the softmax denominator once, with no key
+    # and no value and without the scale
+    sink: bool = False
+    q_temp: Optional[QueryTemperatureSpec] = None
+    # False: the layer has no key / value projections and attends to what the call that
+    # writes its cache entry stored (the run order names that entry)
+    own_kv: bool = True
+
+    @property
+    def v_dim(self) -> int:
+        return self.value_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -70,6 +100,23 @@ class GatedFeedForwardSpec:
     kind: str = "gated_dense"
     intermediate_size: int = 0
     activation: str = "gelu_tanh"
+
+
+@dataclass(frozen=True)
+class RoutedFeedForwardSpec:
+    """A mixture of gated experts, down(act(gate x) * up x) each, of which a token uses
+    ``top``.  Router: s = sigmoid(W_r x) in 32-bit; s + correction chooses, s weighs (not
+    renormalised).  The experts form ``n_groups`` equal groups of neighbours; a group's score
+    is the sum of its two largest choice scores, and only experts of the ``keep_groups`` best
+    groups can be chosen."""
+    kind: str = "routed"
+    n_experts: int = 0
+    top: int = 1
+    intermediate_size: int = 0
+    activation: str = "silu"
+    n_groups: int = 1
+    keep_groups: int = 1
+    correction: bool = True
 
 
 @dataclass(frozen=True)
@@ -86,10 +133,12 @@ class BlockSpec:
     needs other fields.
     """
     mixer: object = None
-    feed_forward: object = None
-    norm: NormSpec = NormSpec()
+    feed_forward: object = None        # None: the layer has no feed-forward branch
+    norm: object = NormSpec()
     arrangement: str = "sandwich"
     kind: str = "sequential"
+    # every branch joins the stream times this: h += residual_mult * post(branch(pre(h)))
+    residual_mult: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -113,7 +162,7 @@ class ModelSpec:
     embed_scale: float
     blocks: Tuple[BlockSpec, ...]
     schedule: Tuple[LayerCall, ...]
-    final_norm: NormSpec
+    final_norm: object
     tie_embeddings: bool = True
     max_positions: int = 0
     bos_token_id: Optional[int] = None
@@ -121,6 +170,8 @@ class ModelSpec:
     # a position encoding that is added to the stream after the embedding (a learned
     # table, say), by its kind in the stream-position registry; None: there is none
     stream_position: Optional[object] = None
+    # logits <- cap * tanh(logits / cap); None: no cap
+    logit_softcap: Optional[float] = None
 
     def n_cache_entries(self) -> int:
         return 1 + max(c.cache for c in self.schedule) if self.schedule else 0

@@ -2,8 +2,9 @@
 its model builder (the reference: ``Arch.detect`` string table,
 src/arch.zig:18-51, and the ``ModelStorage`` union, src/models/model.zig:492-532).
 
-``config.json`` chooses the entry through ``architectures[0]`` or, failing
-that, ``model_type``; an unknown name is an error that lists what is known.
+``config.json`` chooses the entry through ``architectures[0]`` (or the single
+string ``architecture``) or, failing that, ``model_type``; an unknown name is an
+error that lists what is known.
 """
 from __future__ import annotations
 
@@ -40,7 +41,7 @@ def registered_architectures():
 
 def resolve_architecture(raw_config: Dict[str, Any]) -> ArchitectureEntry:
     """The entry that a parsed config.json names."""
-    names = raw_config.get("architectures") or []
+    names = raw_config.get("architectures") or raw_config.get("architecture") or []
     if isinstance(names, str):
         names = [names]
     for n in names:

@@ -88,7 +88,13 @@ struct DecodeArgs {
     int* counters;             // [B * gridDim.y], zero before and after a launch
     int max_pages, page, cap, nh, nkv, hd, window, n_splits, chunk;
     float scale;
+    const float* sinks;        // [nh] sink logits (exp(sink) joins the denominator once), or null
 };
+
+// What the sink of head h adds to a normaliser taken relative to the maximum m.
+__device__ __forceinline__ float sink_term(const DecodeArgs& a, int h, float m) {
+    return a.sinks ? expf(a.sinks[h] - m) : 0.f;
+}
 
 // The decode step's q/k norm, rotation and cache store done by the attention kernel
 // itself (bfloat16 tensor-core form, head sizes 64, 128, 256): with part != null the
@@ -108,6 +114,9 @@ struct FuseQK {
     const float* cosv;         // [B, hd / 2] or null
     const float* sinv;
     int store_kv;
+    float qt_coef;             // != 0: q heads times 1 + qt_coef * ln(floor((p + 1) / qt_every) + 1)
+    int qt_every;
+    int q_only;                // the partial sums hold the query heads alone (nh * hd wide)
 };
 
 // Writes this chunk's (maximum, normaliser), counts the chunk in and, in the
@@ -152,7 +161,7 @@ __device__ __forceinline__ void finish_split(const DecodeArgs& a, int b, int h0,
         L = warp_sum(L);
         if (lane == 0) {
             stat[hh * 2] = M;
-            stat[hh * 2 + 1] = L;
+            stat[hh * 2 + 1] = L + sink_term(a, h0 + hh, M);
         }
     }
     __syncthreads();
@@ -327,7 +336,7 @@ attention_decode_split_kernel(DecodeArgs a) {
         for (int hh = 0; hh < AD_GC; ++hh) {
             if (hh < gc) {
                 if (used == 1) {
-                    const float inv = 1.0f / stat[hh * 2 + 1];
+                    const float inv = 1.0f / (stat[hh * 2 + 1] + sink_term(a, h0 + hh, stat[hh * 2]));
                     outp[hh * hd + d] = from_f32<T>(acc[hh][0] * inv);
                     outp[hh * hd + d + 1] = from_f32<T>(acc[hh][1] * inv);
                 } else {
@@ -454,7 +463,8 @@ __device__ __forceinline__ void dm_head_from_partials(const float* __restrict__ 
                                                       const float* __restrict__ cs,
                                                       const float* __restrict__ sn,
                                                       __nv_bfloat16* tile, int row,
-                                                      __nv_bfloat16* gdst, int lane) {
+                                                      __nv_bfloat16* gdst, int lane,
+                                                      float mul = 1.f) {
     constexpr int HALF = HDP / 64, H2 = HDP / 2;
     const int e0 = lane * HALF;
     float wv[2 * HALF], cv[HALF], sv[HALF];
@@ -492,6 +502,8 @@ __device__ __forceinline__ void dm_head_from_partials(const float* __restrict__ 
 #pragma unroll
         for (int i = 0; i < 2 * HALF; ++i) v[i] = v[i] * rs * wv[i];
     }
+#pragma unroll
+    for (int i = 0; i < 2 * HALF; ++i) v[i] *= mul;
     if (cs) {
 #pragma unroll
         for (int i = 0; i < HALF; ++i) {
@@ -749,7 +761,9 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
     }
     pdl_wait();
     if (has) {
-    const size_t f_width = (size_t)(a.nh + 2 * a.nkv) * hd;  // a row of the projection
+    const size_t f_width = (size_t)(a.nh + (fq.q_only ? 0 : 2 * a.nkv)) * hd;  // a row of the projection
+    const float f_tau = fused && fq.qt_coef != 0.f
+        ? 1.0f + fq.qt_coef * logf((float)((p + 1) / fq.qt_every + 1)) : 1.f;
     const size_t f_stride = (size_t)gridDim.z * f_width;     // one partial sum of the batch
     const float* f_cos = fused && fq.cosv ? fq.cosv + (size_t)b * (hd / 2) : nullptr;
     const float* f_sin = fused && fq.cosv ? fq.sinv + (size_t)b * (hd / 2) : nullptr;
@@ -770,7 +784,8 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
     if (fused)
         for (int r = warp; r < gc; r += DM_THREADS / 32)
             dm_head_from_partials<HDP>(fq.part + (size_t)b * f_width + (size_t)(h0 + r) * hd, fq.G,
-                                       f_stride, fq.wq, fq.eps, f_cos, f_sin, Qs, r, nullptr, lane);
+                                       f_stride, fq.wq, fq.eps, f_cos, f_sin, Qs, r, nullptr, lane,
+                                       f_tau);
     // the new position's key and value: from the cache, or formed here and stored
     auto new_row = [&](T* Ks, T* Vs, int r, int cache_row) {
         if (fused && fq.store_kv) {
@@ -1000,7 +1015,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
                 if (row >= gc) continue;
                 const float v0 = o[i][half * 2], v1 = o[i][half * 2 + 1];
                 if (used == 1) {
-                    const float inv = 1.0f / stat[row * 2 + 1];
+                    const float inv = 1.0f / (stat[row * 2 + 1] + sink_term(a, h0 + row, stat[row * 2]));
                     outp[row * hd + d] = __float2bfloat16_rn(v0 * inv);
                     outp[row * hd + d + 1] = __float2bfloat16_rn(v1 * inv);
                 } else if (cs > 1) {
@@ -1056,7 +1071,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
             }
             if (d < hd) {
                 if (used_clusters == 1) {
-                    outp[row * hd + d] = __float2bfloat16_rn(O / L);
+                    outp[row * hd + d] = __float2bfloat16_rn(O / (L + sink_term(a, h0 + row, M)));
                 } else {
                     a.part_acc[(((size_t)b * a.nh + h0 + row) * a.n_splits + cid) * hd + d] = O;
                     if (d == 0) {
@@ -1263,8 +1278,12 @@ static int attention_decode_impl(const void* q, long long q_stride, void* out, i
                                  const int* slots, const int* positions, int max_pages, int page,
                                  int cap, int B, int nh, int nkv, int hd, float scale, int window,
                                  int max_keys, float* part_acc, float* part_ml, int* counters,
-                                 cudaStream_t stream, const FuseQK& fq) {
+                                 cudaStream_t stream, const FuseQK& fq,
+                                 const float* sinks = nullptr) {
     AGV_REQUIRE(B >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention_decode: bad sizes");
+    AGV_REQUIRE(!fq.q_only || !fq.store_kv, "attention_decode: queries alone bring nothing to store");
+    AGV_REQUIRE(fq.qt_coef == 0.f || fq.qt_every > 0, "attention_decode: the query temperature "
+                "needs a period >= 1");
     AGV_REQUIRE(nh % nkv == 0, "attention_decode: %d heads are not a multiple of %d kv heads", nh,
                 nkv);
     const int elem = dtype == AGV_F32 ? 4 : 2;
@@ -1286,7 +1305,7 @@ static int attention_decode_impl(const void* q, long long q_stride, void* out, i
     AGV_REQUIRE(smem <= (size_t)AD_MAX_SMEM, "attention_decode: %zu bytes of shared memory needed",
                 smem);
     DecodeArgs a{q, q_stride, out, k_pool, v_pool, page_table, slots, positions, part_acc, part_ml,
-                 counters, max_pages, page, cap, nh, nkv, hd, window, n_splits, ch, scale};
+                 counters, max_pages, page, cap, nh, nkv, hd, window, n_splits, ch, scale, sinks};
     if (dtype == AGV_BF16 && hd % 8 == 0 && hd <= 256 && ch == DM_KEYS &&
         (fq.part || (q_stride % 8 == 0 && agv_aligned(q, 16)))) {
         if (hd <= 64) return launch_decode_form<64>(a, B, stream, fq);
@@ -1330,6 +1349,18 @@ AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, i
                                  max_keys, part_acc, part_ml, counters, stream, FuseQK{});
 }
 
+// The same with a sink logit per query head ([nh] 32-bit, or null).
+AGV_API int agv_attention_decode_ex(const void* q, long long q_stride, void* out, int dtype,
+                                    const void* k_pool, const void* v_pool, const int* page_table,
+                                    const int* slots, const int* positions, int max_pages, int page,
+                                    int cap, int B, int nh, int nkv, int hd, float scale, int window,
+                                    int max_keys, float* part_acc, float* part_ml, int* counters,
+                                    const float* sinks, cudaStream_t stream) {
+    return attention_decode_impl(q, q_stride, out, dtype, k_pool, v_pool, page_table, slots,
+                                 positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,
+                                 max_keys, part_acc, part_ml, counters, stream, FuseQK{}, sinks);
+}
+
 // Whether agv_attention_decode_fused takes these sizes: bfloat16, head sizes 64, 128,
 // 256, the whole head rotated (or none of it).
 AGV_API int agv_attention_decode_fused_supported(int dtype, int hd, int rotary_dim) {
@@ -1356,10 +1387,34 @@ AGV_API int agv_attention_decode_fused(const float* part, int G, const float* wq
                 "attention_decode_fused: head_dim %d is not 64, 128 or 256", hd);
     AGV_REQUIRE(!cosv || sinv, "attention_decode_fused: cos without sin");
     AGV_REQUIRE(agv_aligned(part, 16), "attention_decode_fused: partial sums must be aligned");
-    FuseQK fq{part, G, wq, wk, eps, cosv, sinv, store_kv};
+    FuseQK fq{part, G, wq, wk, eps, cosv, sinv, store_kv, 0.f, 1, 0};
     return attention_decode_impl(nullptr, 0, out, AGV_BF16, k_pool, v_pool, page_table, slots,
                                  positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,
                                  max_keys, part_acc, part_ml, counters, stream, fq);
+}
+
+// The fused form with the options of a layer that has them: a sink logit per query head
+// (sinks [nh] or null), a query temperature (qt_coef != 0), and partial sums that hold the
+// query heads alone (q_only: the layer attends to keys and values another layer stored).
+AGV_API int agv_attention_decode_fused_ex(const float* part, int G, const float* wq,
+                                          const float* wk, float eps, const float* cosv,
+                                          const float* sinv, int store_kv, void* out,
+                                          const void* k_pool, const void* v_pool,
+                                          const int* page_table, const int* slots,
+                                          const int* positions, int max_pages, int page, int cap,
+                                          int B, int nh, int nkv, int hd, float scale, int window,
+                                          int max_keys, float* part_acc, float* part_ml,
+                                          int* counters, const float* sinks, float qt_coef,
+                                          int qt_every, int q_only, cudaStream_t stream) {
+    AGV_REQUIRE(agv_attention_decode_fused_supported(AGV_BF16, hd, cosv ? hd : 0),
+                "attention_decode_fused: head_dim %d is not 64, 128 or 256", hd);
+    AGV_REQUIRE(part && G >= 1, "attention_decode_fused: no partial sums");
+    AGV_REQUIRE(agv_aligned(part, 16), "attention_decode_fused: partial sums must be 16-byte aligned");
+    FuseQK fq{part, G, wq, wk, eps, cosv, sinv, store_kv, qt_coef, qt_every > 0 ? qt_every : 1,
+              q_only};
+    return attention_decode_impl(nullptr, 0, out, AGV_BF16, k_pool, v_pool, page_table, slots,
+                                 positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,
+                                 max_keys, part_acc, part_ml, counters, stream, fq, sinks);
 }
 
 // ------------------------------------------------------- no-allocation variant

@@ -83,7 +83,8 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
                              const __nv_bfloat16* __restrict__ k,
                              const __nv_bfloat16* __restrict__ v, long long kv_stride,
                              __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_seqlens,
-                             int nh, int nkv, int hd, float scale_log2e, int window) {
+                             int nh, int nkv, int hd, float scale_log2e, int window,
+                             const float* __restrict__ sinks) {
     pdl_wait();
     pdl_launch_next();
     constexpr int FA_M = NW * 16, FA_THREADS = NW * 32;
@@ -211,6 +212,13 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
         row_l[rr] += __shfl_xor_sync(0xffffffffu, row_l[rr], 1);
         row_l[rr] += __shfl_xor_sync(0xffffffffu, row_l[rr], 2);
     }
+    if (sinks) {
+        // the head's sink logit joins the denominator once, on the running maximum's scale
+        const float sk = sinks[h] * 1.4426950408889634f;
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr)
+            if (row_m[rr] != -INFINITY) row_l[rr] += exp2f(sk - row_m[rr]);
+    }
     const float inv0 = row_l[0] > 0.f ? 1.0f / row_l[0] : 0.f;
     const float inv1 = row_l[1] > 0.f ? 1.0f / row_l[1] : 0.f;
     __nv_bfloat16* ob = out + (size_t)seq0 * (size_t)(nh * hd) + (size_t)h * hd;
@@ -231,7 +239,7 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
 template <int HDP, int NW>
 int launch_fa(const void* q, long long q_stride, const void* k, const void* v, long long kv_stride,
               void* out, const int* cu_seqlens, int B, int max_len, int nh, int nkv, int hd,
-              float scale, int window, cudaStream_t stream) {
+              float scale, int window, cudaStream_t stream, const float* sinks) {
     auto kern = attention_prefill_mma_kernel<HDP, NW>;
     constexpr int FA_M = NW * 16, FA_THREADS = NW * 32;
     constexpr int smem = (FA_M + 2 * FA_N) * HDP * 2;
@@ -243,7 +251,7 @@ int launch_fa(const void* q, long long q_stride, const void* k, const void* v, l
     dim3 grid((max_len + FA_M - 1) / FA_M, nh, B);
     agv_launch(kern, grid, FA_THREADS, smem, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
         kv_stride, (__nv_bfloat16*)out, cu_seqlens, nh, nkv, hd,
-        scale * 1.4426950408889634f, window);
+        scale * 1.4426950408889634f, window, sinks);
     AGV_LAUNCH_OK("attention_prefill_mma_kernel");
     return 0;
 }
@@ -260,10 +268,12 @@ AGV_API int agv_attention_prefill_mma_supported(int hd, long long q_stride, long
 // stride q_stride; k, v: [T, nkv, hd] rows of stride kv_stride; out: [T, nh * hd]
 // dense; cu_seqlens: [B + 1] first token of each sequence; max_len: the
 // greatest sequence length (sizes the grid).  window 0: no window.
-AGV_API int agv_attention_prefill_mma(const void* q, long long q_stride, const void* k,
-                                      const void* v, long long kv_stride, void* out,
-                                      const int* cu_seqlens, int B, int max_len, int nh, int nkv,
-                                      int hd, float scale, int window, cudaStream_t stream) {
+// sinks: [nh] sink logits (exp(sink) joins each row's softmax denominator once), or null.
+AGV_API int agv_attention_prefill_mma_ex(const void* q, long long q_stride, const void* k,
+                                         const void* v, long long kv_stride, void* out,
+                                         const int* cu_seqlens, int B, int max_len, int nh, int nkv,
+                                         int hd, float scale, int window, const float* sinks,
+                                         cudaStream_t stream) {
     AGV_REQUIRE(B >= 0 && nh > 0 && nkv > 0 && hd > 0 && max_len >= 0, "attention: bad sizes");
     AGV_REQUIRE(nh % nkv == 0, "attention: %d heads are not a multiple of %d kv heads", nh, nkv);
     AGV_REQUIRE(agv_attention_prefill_mma_supported(hd, q_stride, kv_stride),
@@ -279,11 +289,19 @@ AGV_API int agv_attention_prefill_mma(const void* q, long long q_stride, const v
     const bool wide = false;
 #define AGV_FA(HDP)                                                                             \
     return wide ? launch_fa<HDP, 8>(q, q_stride, k, v, kv_stride, out, cu_seqlens, B, max_len,  \
-                                    nh, nkv, hd, scale, window, stream)                          \
+                                    nh, nkv, hd, scale, window, stream, sinks)                   \
                 : launch_fa<HDP, 4>(q, q_stride, k, v, kv_stride, out, cu_seqlens, B, max_len,  \
-                                    nh, nkv, hd, scale, window, stream)
+                                    nh, nkv, hd, scale, window, stream, sinks)
     if (hd <= 64) AGV_FA(64);
     if (hd <= 128) AGV_FA(128);
     AGV_FA(256);
 #undef AGV_FA
+}
+
+AGV_API int agv_attention_prefill_mma(const void* q, long long q_stride, const void* k,
+                                      const void* v, long long kv_stride, void* out,
+                                      const int* cu_seqlens, int B, int max_len, int nh, int nkv,
+                                      int hd, float scale, int window, cudaStream_t stream) {
+    return agv_attention_prefill_mma_ex(q, q_stride, k, v, kv_stride, out, cu_seqlens, B, max_len,
+                                        nh, nkv, hd, scale, window, nullptr, stream);
 }

@@ -57,6 +57,7 @@ struct AtArgs {
     float scale_log2e;
     int kb;                        // 64-element blocks of head_dim
     int tmem_cols;
+    const float* sinks;            // [nh] sink logits joining each row's denominator once, or null
 };
 
 // 2^x by the hardware approximation (relative error about 2^-22; -inf gives 0).
@@ -414,6 +415,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 give_up(3, 3);
             } else {
                 tc_fence_after();
+                if (a.sinks && m_used != -INFINITY)
+                    l += exp2f(a.sinks[head0 + hl] * 1.4426950408889634f - m_used);
                 const float inv = l > 0.f ? 1.0f / l : 0.f;
                 __nv_bfloat16* dst = a.out + (size_t)(seq0 + qp) * ((size_t)a.nh * a.hd) +
                                      (size_t)(head0 + hl) * a.hd;
@@ -541,11 +544,13 @@ AGV_API int agv_transpose_values(const void* v, long long kv_stride, void* vt, l
 // max_len: the greatest sequence length (sizes the grid).  window 0: no window.
 // vt_ready != 0: vt already holds the transposed values (agv_qk_norm_rope_store
 // wrote them); else they are transposed here first.
-AGV_API int agv_attention_prefill_tc(const void* q, long long q_stride, const void* k,
-                                     const void* v, long long kv_stride, void* out, void* vt,
-                                     long long vt_cols, int vt_ready, const int* cu_seqlens, int B,
-                                     int T, int max_len, int nh, int nkv, int hd, float scale,
-                                     int window, cudaStream_t stream) {
+// sinks: [nh] sink logits or null; the scale must be positive.
+AGV_API int agv_attention_prefill_tc_ex(const void* q, long long q_stride, const void* k,
+                                        const void* v, long long kv_stride, void* out, void* vt,
+                                        long long vt_cols, int vt_ready, const int* cu_seqlens, int B,
+                                        int T, int max_len, int nh, int nkv, int hd, float scale,
+                                        int window, const float* sinks, cudaStream_t stream) {
+    AGV_REQUIRE(scale > 0.f, "attention: the tcgen05 kernel takes a positive score scale");
     AGV_REQUIRE(B >= 0 && T >= 0 && nh > 0 && nkv > 0 && hd > 0 && max_len >= 0,
                 "attention: bad sizes");
     AGV_REQUIRE(nh % nkv == 0, "attention: %d heads are not a multiple of %d kv heads", nh, nkv);
@@ -572,6 +577,7 @@ AGV_API int agv_attention_prefill_tc(const void* q, long long q_stride, const vo
     a.scale_log2e = scale * 1.4426950408889634f;
     a.kb = (hd + 63) / 64;
     a.tmem_cols = AT_O_COL + hd <= 256 ? 256 : 512;
+    a.sinks = sinks;
 
     CUtensorMap mq, mk, mvt;
     {
@@ -610,4 +616,14 @@ AGV_API int agv_attention_prefill_tc(const void* q, long long q_stride, const vo
     agv_launch(attention_prefill_tc_kernel, grid, AT_THREADS, smem, stream, mq, mk, mvt, a);
     AGV_LAUNCH_OK("attention_prefill_tc_kernel");
     return 0;
+}
+
+AGV_API int agv_attention_prefill_tc(const void* q, long long q_stride, const void* k,
+                                     const void* v, long long kv_stride, void* out, void* vt,
+                                     long long vt_cols, int vt_ready, const int* cu_seqlens, int B,
+                                     int T, int max_len, int nh, int nkv, int hd, float scale,
+                                     int window, cudaStream_t stream) {
+    return agv_attention_prefill_tc_ex(q, q_stride, k, v, kv_stride, out, vt, vt_cols, vt_ready,
+                                       cu_seqlens, B, T, max_len, nh, nkv, hd, scale, window,
+                                       nullptr, stream);
 }

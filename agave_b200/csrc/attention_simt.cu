@@ -10,6 +10,10 @@
 // sl - W for sl = p + 1 > W (src/models/gemma4.zig:1153-1155).  No value row is
 // skipped for a small weight (the reference skips below 1e-6,
 // src/backend/kernels/cuda/sdpa.zig:14,99).
+//
+// Two options beyond that: a value head size hdv that differs from the query / key head
+// size hd, and a sink per query head: a learned logit with no key and no value that
+// adds exp(sink) to the softmax denominator once (it is not scaled).
 #include "common.cuh"
 
 constexpr int AT_WARPS = 4;
@@ -29,7 +33,8 @@ attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T* __re
                       const T* __restrict__ v, long long kv_stride, T* __restrict__ out,
                       const int* __restrict__ positions, const int* __restrict__ seq_index,
                       const int* __restrict__ cu_seqlens, PagedKV pk, int n_tokens, int nh, int nkv,
-                      int hd, float scale, int window) {
+                      int hd, float scale, int window, int hdv, long long v_stride,
+                      const float* __restrict__ sinks) {
     pdl_wait();
     pdl_launch_next();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -38,12 +43,12 @@ attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T* __re
     const int t = (int)(item / nh), h = (int)(item % nh);
     const int g = h / (nh / nkv);
     const int b = seq_index[t];
-    T* o = out + ((size_t)t * nh + h) * hd;
+    T* o = out + ((size_t)t * nh + h) * hdv;
     int slot = 0;
     if (PAGED) {
         slot = pk.slots[b];
         if (slot < 0) {
-            for (int e = lane; e < hd; e += 32) o[e] = from_f32<T>(0.f);
+            for (int e = lane; e < hdv; e += 32) o[e] = from_f32<T>(0.f);
             return;
         }
     }
@@ -64,12 +69,12 @@ attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T* __re
         if (PAGED) {
             const int row = j % pk.cap;
             const int page = pk.page_table[(size_t)slot * pk.max_pages + row / pk.page];
-            const size_t off = (((size_t)page * pk.page + row % pk.page) * nkv + g) * hd;
-            kp = (const T*)pk.k_pool + off;
-            vp = (const T*)pk.v_pool + off;
+            const size_t off = ((size_t)page * pk.page + row % pk.page) * nkv + g;
+            kp = (const T*)pk.k_pool + off * hd;
+            vp = (const T*)pk.v_pool + off * hdv;
         } else {
             kp = k + (base + j) * kv_stride + (size_t)g * hd;
-            vp = v + (base + j) * kv_stride + (size_t)g * hd;
+            vp = v + (base + j) * v_stride + (size_t)g * hdv;
         }
         float s = 0.f;
 #pragma unroll
@@ -85,19 +90,30 @@ attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T* __re
 #pragma unroll
         for (int i = 0; i < AT_MAX_I; ++i) {
             const int e = lane + 32 * i;
-            if (e < hd) acc[i] = acc[i] * alpha + w * to_f32(vp[e]);
+            if (e < hdv) acc[i] = acc[i] * alpha + w * to_f32(vp[e]);
         }
         m = mn;
+    }
+    if (sinks) {
+        // the sink joins the denominator as one more term, on the running maximum's scale
+        const float sk = sinks[h];
+        const float mn = fmaxf(m, sk);
+        const float alpha = expf(m - mn);
+        l = l * alpha + expf(sk - mn);
+#pragma unroll
+        for (int i = 0; i < AT_MAX_I; ++i) acc[i] *= alpha;
     }
     const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
     for (int i = 0; i < AT_MAX_I; ++i) {
         const int e = lane + 32 * i;
-        if (e < hd) o[e] = from_f32<T>(acc[i] * inv);
+        if (e < hdv) o[e] = from_f32<T>(acc[i] * inv);
     }
 }
 
-static int check_attn(int n_tokens, int nh, int nkv, int hd, int window) {
+static int check_attn(int n_tokens, int nh, int nkv, int hd, int window, int hdv = 1) {
+    AGV_REQUIRE(hdv > 0 && hdv <= 32 * AT_MAX_I, "attention: value head size %d outside 1..%d", hdv,
+                32 * AT_MAX_I);
     AGV_REQUIRE(n_tokens >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention: bad sizes");
     AGV_REQUIRE(nh % nkv == 0, "attention: %d heads are not a multiple of %d kv heads", nh, nkv);
     AGV_REQUIRE(hd <= 32 * AT_MAX_I, "attention: head_dim %d exceeds %d", hd, 32 * AT_MAX_I);
@@ -110,39 +126,56 @@ static int check_attn(int n_tokens, int nh, int nkv, int hd, int window) {
 // the fused projection output); out: [T, nh * hd] dense.  Token t of batch
 // entry b = seq_index[t] has position positions[t] and sees the tokens
 // cu_seqlens[b] + j for lo <= j <= position.  window 0: no window.
-AGV_API int agv_attention_prefill_simt(const void* q, long long q_stride, const void* k,
-                                       const void* v, long long kv_stride, void* out, int dtype,
-                                       const int* positions, const int* seq_index,
-                                       const int* cu_seqlens, int n_tokens, int nh, int nkv, int hd,
-                                       float scale, int window, cudaStream_t stream) {
-    if (int rc = check_attn(n_tokens, nh, nkv, hd, window)) return rc;
+// hdv: the value head size (v: [T, nkv, hdv] with row stride v_stride, out: [T, nh * hdv]);
+// sinks: [nh] 32-bit sink logits or null.
+AGV_API int agv_attention_prefill_simt_ex(const void* q, long long q_stride, const void* k,
+                                          const void* v, long long kv_stride, void* out, int dtype,
+                                          const int* positions, const int* seq_index,
+                                          const int* cu_seqlens, int n_tokens, int nh, int nkv,
+                                          int hd, float scale, int window, int hdv,
+                                          long long v_stride, const float* sinks,
+                                          cudaStream_t stream) {
+    if (int rc = check_attn(n_tokens, nh, nkv, hd, window, hdv)) return rc;
     if (n_tokens == 0) return 0;
     const long long items = (long long)n_tokens * nh;
     const unsigned grid = (unsigned)((items + AT_WARPS - 1) / AT_WARPS);
     PagedKV pk{};
     if (dtype == AGV_F32)
         agv_launch(attention_simt_kernel<float, false>, grid, AT_WARPS * 32, 0, stream, (const float*)q, q_stride, (const float*)k, (const float*)v, kv_stride, (float*)out,
-            positions, seq_index, cu_seqlens, pk, n_tokens, nh, nkv, hd, scale, window);
+            positions, seq_index, cu_seqlens, pk, n_tokens, nh, nkv, hd, scale, window, hdv,
+            v_stride, sinks);
     else if (dtype == AGV_BF16)
         agv_launch(attention_simt_kernel<__nv_bfloat16, false>, grid, AT_WARPS * 32, 0, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
             kv_stride, (__nv_bfloat16*)out, positions, seq_index, cu_seqlens, pk, n_tokens, nh,
-            nkv, hd, scale, window);
+            nkv, hd, scale, window, hdv, v_stride, sinks);
     else
         return agv_fail(-1, "attention: unknown dtype %d", dtype);
     AGV_LAUNCH_OK("attention_simt_kernel");
     return 0;
 }
 
+AGV_API int agv_attention_prefill_simt(const void* q, long long q_stride, const void* k,
+                                       const void* v, long long kv_stride, void* out, int dtype,
+                                       const int* positions, const int* seq_index,
+                                       const int* cu_seqlens, int n_tokens, int nh, int nkv, int hd,
+                                       float scale, int window, cudaStream_t stream) {
+    return agv_attention_prefill_simt_ex(q, q_stride, k, v, kv_stride, out, dtype, positions,
+                                         seq_index, cu_seqlens, n_tokens, nh, nkv, hd, scale,
+                                         window, hd, kv_stride, nullptr, stream);
+}
+
 // Queries against the paged cache (the query's own key is already stored).
 // Token t of entry b = seq_index[t] at positions[t] sees cache positions
 // lo..positions[t] of slot slots[b]; a negative slot yields zeros.
-AGV_API int agv_attention_paged_simt(const void* q, long long q_stride, void* out, int dtype,
-                                     const void* k_pool, const void* v_pool, const int* page_table,
-                                     const int* slots, const int* positions, const int* seq_index,
-                                     int max_pages, int page, int cap, int n_tokens, int nh,
-                                     int nkv, int hd, float scale, int window,
-                                     cudaStream_t stream) {
-    if (int rc = check_attn(n_tokens, nh, nkv, hd, window)) return rc;
+// hdv: the value head size (v_pool rows of nkv * hdv, out: [T, nh * hdv]); sinks: [nh] or null.
+AGV_API int agv_attention_paged_simt_ex(const void* q, long long q_stride, void* out, int dtype,
+                                        const void* k_pool, const void* v_pool,
+                                        const int* page_table, const int* slots,
+                                        const int* positions, const int* seq_index, int max_pages,
+                                        int page, int cap, int n_tokens, int nh, int nkv, int hd,
+                                        float scale, int window, int hdv, const float* sinks,
+                                        cudaStream_t stream) {
+    if (int rc = check_attn(n_tokens, nh, nkv, hd, window, hdv)) return rc;
     AGV_REQUIRE(page > 0 && cap > 0 && max_pages > 0, "attention: bad cache geometry");
     AGV_REQUIRE(window == 0 || window <= cap, "attention: window %d exceeds the ring of %d rows",
                 window, cap);
@@ -152,12 +185,23 @@ AGV_API int agv_attention_paged_simt(const void* q, long long q_stride, void* ou
     PagedKV pk{k_pool, v_pool, page_table, slots, max_pages, page, cap};
     if (dtype == AGV_F32)
         agv_launch(attention_simt_kernel<float, true>, grid, AT_WARPS * 32, 0, stream, (const float*)q, q_stride, nullptr, nullptr, 0, (float*)out, positions, seq_index,
-            nullptr, pk, n_tokens, nh, nkv, hd, scale, window);
+            nullptr, pk, n_tokens, nh, nkv, hd, scale, window, hdv, 0LL, sinks);
     else if (dtype == AGV_BF16)
         agv_launch(attention_simt_kernel<__nv_bfloat16, true>, grid, AT_WARPS * 32, 0, stream, (const __nv_bfloat16*)q, q_stride, nullptr, nullptr, 0, (__nv_bfloat16*)out, positions,
-            seq_index, nullptr, pk, n_tokens, nh, nkv, hd, scale, window);
+            seq_index, nullptr, pk, n_tokens, nh, nkv, hd, scale, window, hdv, 0LL, sinks);
     else
         return agv_fail(-1, "attention: unknown dtype %d", dtype);
     AGV_LAUNCH_OK("attention_simt_kernel");
     return 0;
+}
+
+AGV_API int agv_attention_paged_simt(const void* q, long long q_stride, void* out, int dtype,
+                                     const void* k_pool, const void* v_pool, const int* page_table,
+                                     const int* slots, const int* positions, const int* seq_index,
+                                     int max_pages, int page, int cap, int n_tokens, int nh,
+                                     int nkv, int hd, float scale, int window,
+                                     cudaStream_t stream) {
+    return agv_attention_paged_simt_ex(q, q_stride, out, dtype, k_pool, v_pool, page_table, slots,
+                                       positions, seq_index, max_pages, page, cap, n_tokens, nh,
+                                       nkv, hd, scale, window, hd, nullptr, stream);
 }

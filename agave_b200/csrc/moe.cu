@@ -1,0 +1,329 @@
+// Routed feed-forward (mixture of experts): router, the plan that sorts (token, choice)
+// pairs by expert, and the experts' products run as grouped products over that plan.
+//
+// Router (32-bit): z = W_r x, s = sigmoid(z), choice score c = s + correction.  The experts
+// lie in n_groups equal groups of neighbours; a group's score is the sum of its two largest
+// c; only the experts of the `keep` best groups can be chosen (the others count as minus
+// infinity); the `top` largest c among them win, and their weights are their s, as they
+// are.  n_groups = keep = 1 is plain top-k routing; correction null adds nothing.  Ties go
+// to the lower index.
+//
+// Plan: the P = T * top pairs are laid out by expert, every expert's run padded to a
+// multiple of the row tile, so that a tile of the grouped products belongs to one expert.
+// Everything is sized on the host from upper bounds (P + E * tile rows, P / tile + E tiles)
+// and decided on the device: nothing is read back, so a step records into a CUDA graph.
+//
+// Grouped products: out[pos, :] = a[src(pos), :] * W[e(tile)]^T, plain, or the gated pair
+// act(a Wg^T) * (a Wu^T); a row of the result can be scaled and scattered (the down
+// product leaves w_pair * y at [choice, token, :], which the join that follows adds over
+// the choices in order).  Each output element is one dot product accumulated in ascending
+// k in 32-bit: a token's result does not depend on its company.
+#include "common.cuh"
+
+namespace {
+
+enum { MOE_ACT_GELU_TANH = 0, MOE_ACT_SILU = 1 };
+
+__device__ __forceinline__ float moe_act(float t, int act) {
+    if (act == MOE_ACT_SILU) return t / (1.0f + expf(-t));
+    const float u = 0.7978845608028654f * (t + 0.044715f * t * t * t);
+    return 0.5f * t * (1.0f + tanhf(u));
+}
+
+constexpr int RT_WARPS = 4;
+constexpr int RT_MAX_E = 512;
+
+// One warp per token: logits by lanes over H, then lane 0 chooses.
+template <typename T>
+__global__ void __launch_bounds__(RT_WARPS * 32)
+moe_route_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ wr,
+                 const float* __restrict__ correction, int n_tokens, int H, int E, int n_groups,
+                 int keep, int top, int* __restrict__ ids, float* __restrict__ wts) {
+    pdl_wait();
+    pdl_launch_next();
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * RT_WARPS + warp;
+    if (t >= n_tokens) return;
+    float* s = smem + (size_t)warp * 2 * E;      // sigmoid scores
+    float* c = s + E;                            // choice scores (consumed by the choice)
+    const T* xr = x + (size_t)t * ldx;
+    for (int e = 0; e < E; ++e) {
+        const T* w = wr + (size_t)e * H;
+        float z = 0.f;
+        for (int i = lane; i < H; i += 32) z = fmaf(to_f32(xr[i]), to_f32(w[i]), z);
+        z = warp_sum(z);
+        if (lane == 0) {
+            const float sg = 1.0f / (1.0f + expf(-z));
+            s[e] = sg;
+            c[e] = sg + (correction ? correction[e] : 0.f);
+        }
+    }
+    __syncwarp();
+    if (lane != 0) return;
+    const int per = E / n_groups;
+    if (keep < n_groups) {
+        // group scores: the two largest choice scores of each group, summed
+        unsigned long long kept[RT_MAX_E / 64] = {};
+        for (int k = 0; k < keep; ++k) {
+            int best = -1;
+            float best_v = -INFINITY;
+            for (int g = 0; g < n_groups; ++g) {
+                if (kept[g >> 6] >> (g & 63) & 1ull) continue;
+                float a = -INFINITY, b = -INFINITY;          // largest, second largest
+                for (int i = 0; i < per; ++i) {
+                    const float v = c[g * per + i];
+                    if (v > a) { b = a; a = v; }
+                    else if (v > b) b = v;
+                }
+                const float sc = per > 1 ? a + b : a;
+                if (best < 0 || sc > best_v) { best = g; best_v = sc; }
+            }
+            kept[best >> 6] |= 1ull << (best & 63);
+        }
+        for (int g = 0; g < n_groups; ++g)
+            if (!(kept[g >> 6] >> (g & 63) & 1ull))
+                for (int i = 0; i < per; ++i) c[g * per + i] = -INFINITY;
+    }
+    for (int k = 0; k < top; ++k) {
+        int best = -1;
+        float best_v = -INFINITY;
+        for (int e = 0; e < E; ++e) {
+            const float v = c[e];
+            if (v > best_v) { best = e; best_v = v; }
+        }
+        if (best < 0) best = 0;                 // (no finite score left: cannot happen with finite inputs)
+        ids[(size_t)t * top + k] = best;
+        wts[(size_t)t * top + k] = s[best];
+        c[best] = -INFINITY;
+    }
+}
+
+// One CTA lays the pairs out by expert.  tile: rows per tile of the grouped products.
+//   tok[pos]    token of the pair at sorted position pos, -1 for padding
+//   dst[pos]    choice * T + token: the row the down product writes
+//   wpos[pos]   the pair's weight
+//   pos_of[p]   where pair p went (for consumers that walk pairs)
+//   tile_e[i]   expert of tile i, -1 for tiles beyond the last
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int n_tokens, int top,
+                int E, int tile, int* __restrict__ tok, int* __restrict__ dst,
+                float* __restrict__ wpos, int* __restrict__ pos_of, int* __restrict__ tile_e,
+                int max_rows, int max_tiles) {
+    pdl_launch_next();
+    extern __shared__ int sm[];
+    int* count = sm;              // [E]
+    int* start = sm + E;          // [E + 1] first row of each expert's run
+    const int P = n_tokens * top;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    pdl_wait();
+    for (int i = threadIdx.x; i < max_rows; i += blockDim.x) tok[i] = -1;
+    for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&count[ids[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) {
+            start[e] = at;
+            at += (count[e] + tile - 1) / tile * tile;
+        }
+        start[E] = at;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) {
+        const int row0 = i * tile;
+        int e = -1;
+        if (row0 < start[E]) {
+            // the expert whose run holds row0 (runs are in expert order; E is small)
+            int lo = 0, hi = E - 1;
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (start[mid] <= row0) lo = mid; else hi = mid - 1;
+            }
+            e = lo;          // (the last of the experts that start here: the others' runs are empty)
+        }
+        tile_e[i] = e;
+    }
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;     // now the cursors
+    __syncthreads();
+    // a pair takes the next free row of its expert's run; the order inside a run is
+    // whatever the atomics make it, which no result depends on (rows are independent)
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int e = ids[p];
+        const int pos = start[e] + atomicAdd(&count[e], 1);
+        tok[pos] = p / top;
+        dst[pos] = (p % top) * n_tokens + p / top;
+        wpos[pos] = wts[p];
+        pos_of[p] = pos;
+    }
+}
+
+constexpr int GM = 64, GN = 64, GK = 16;
+
+// A tile of 64 sorted rows x 64 output features of one expert.  A rows are gathered through
+// a_index (null: row = pos, live where tok[pos] >= 0); C rows go to c_index[pos] (null:
+// pos) times c_scale[pos] (null: 1).
+template <typename TA, typename TW, typename TO, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_grouped_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ a_index,
+                   const int* __restrict__ tok, const TW* __restrict__ W,
+                   const TW* __restrict__ W2, TO* __restrict__ C, long long ldc,
+                   const int* __restrict__ c_index, const float* __restrict__ c_scale,
+                   const int* __restrict__ tile_e, int N, int K, int act) {
+    pdl_wait();
+    pdl_launch_next();
+    const int e = tile_e[blockIdx.y];
+    if (e < 0) return;
+    __shared__ float As[GK][GM + 4];
+    __shared__ float Ws[GK][GN + 4];
+    __shared__ float Us[GATED ? GK : 1][GATED ? GN + 4 : 1];
+    __shared__ int arow[GM];
+    const int tid = threadIdx.x;
+    const int tx = tid % 16, ty = tid / 16;
+    const int m0 = blockIdx.y * GM, n0 = blockIdx.x * GN;
+    if (tid < GM) {
+        const int pos = m0 + tid;
+        const int t = tok[pos];
+        arow[tid] = t < 0 ? -1 : (a_index ? a_index[pos] : pos);
+    }
+    __syncthreads();
+    const TW* We = W + (size_t)e * N * K;
+    const TW* We2 = GATED ? W2 + (size_t)e * N * K : nullptr;
+    float acc[4][4] = {};
+    float acc2[GATED ? 4 : 1][GATED ? 4 : 1] = {};
+    const int lr = tid / 4, lk = (tid % 4) * 4;
+    const int ar = arow[lr];
+    for (int k0 = 0; k0 < K; k0 += GK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int k = k0 + lk + i;
+            const int n = n0 + lr;
+            As[lk + i][lr] = (ar >= 0 && k < K) ? to_f32(A[(size_t)ar * lda + k]) : 0.f;
+            Ws[lk + i][lr] = (n < N && k < K) ? to_f32(We[(size_t)n * K + k]) : 0.f;
+            if (GATED) Us[lk + i][lr] = (n < N && k < K) ? to_f32(We2[(size_t)n * K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < GK; ++k) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+            if (GATED) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) b[j] = Us[k][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc2[i][j] = fmaf(a[i], b[j], acc2[i][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        if (arow[r] < 0) continue;
+        const int pos = m0 + r;
+        const size_t crow = c_index ? (size_t)c_index[pos] : (size_t)pos;
+        const float sc = c_scale ? c_scale[pos] : 1.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (GATED) v = moe_act(v, act) * acc2[i][j];
+            C[crow * ldc + n] = from_f32<TO>(v * sc);
+        }
+    }
+}
+
+}  // namespace
+
+// x: [T, H] rows of stride ldx, wr: [E, H] (both `dtype`); correction: [E] 32-bit or null;
+// ids, wts: [T, top] outputs.
+AGV_API int agv_moe_route(const void* x, long long ldx, const void* wr, const float* correction,
+                          int dtype, int T, int H, int E, int n_groups, int keep, int top,
+                          int* ids, float* wts, cudaStream_t stream) {
+    AGV_REQUIRE(T >= 0 && H > 0 && E > 0 && top > 0, "moe_route: bad sizes");
+    AGV_REQUIRE(E <= RT_MAX_E, "moe_route: %d experts exceed %d", E, RT_MAX_E);
+    AGV_REQUIRE(n_groups >= 1 && E % n_groups == 0, "moe_route: %d experts do not form %d equal "
+                "groups", E, n_groups);
+    AGV_REQUIRE(keep >= 1 && keep <= n_groups, "moe_route: keep %d outside 1..%d", keep, n_groups);
+    AGV_REQUIRE(top <= keep * (E / n_groups), "moe_route: top %d exceeds the %d experts of the "
+                "groups kept", top, keep * (E / n_groups));
+    AGV_REQUIRE(ldx >= H, "moe_route: row stride shorter than a row");
+    if (T == 0) return 0;
+    const unsigned grid = (unsigned)((T + RT_WARPS - 1) / RT_WARPS);
+    const size_t smem = (size_t)RT_WARPS * 2 * E * sizeof(float);
+    if (dtype == AGV_F32)
+        agv_launch(moe_route_kernel<float>, grid, RT_WARPS * 32, smem, stream, (const float*)x, ldx,
+                   (const float*)wr, correction, T, H, E, n_groups, keep, top, ids, wts);
+    else if (dtype == AGV_BF16)
+        agv_launch(moe_route_kernel<__nv_bfloat16>, grid, RT_WARPS * 32, smem, stream,
+                   (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)wr, correction, T, H, E,
+                   n_groups, keep, top, ids, wts);
+    else
+        return agv_fail(-1, "moe_route: unknown dtype %d", dtype);
+    AGV_LAUNCH_OK("moe_route_kernel");
+    return 0;
+}
+
+AGV_API int agv_moe_tile_rows() { return GM; }
+
+// Upper bounds the caller sizes the plan's arrays with.
+AGV_API int agv_moe_plan_tiles(int T, int top, int E) { return (T * top + GM - 1) / GM + E; }
+AGV_API int agv_moe_plan_rows(int T, int top, int E) { return agv_moe_plan_tiles(T, top, E) * GM; }
+
+// See moe_plan_kernel; tok, dst, wpos: [agv_moe_plan_rows], pos_of: [T * top],
+// tile_e: [agv_moe_plan_tiles].
+AGV_API int agv_moe_plan(const int* ids, const float* wts, int T, int top, int E, int* tok,
+                         int* dst, float* wpos, int* pos_of, int* tile_e, cudaStream_t stream) {
+    AGV_REQUIRE(T >= 0 && top > 0 && E > 0, "moe_plan: bad sizes");
+    AGV_REQUIRE(E <= 4096, "moe_plan: %d experts exceed 4096", E);
+    if (T == 0) return 0;
+    const size_t smem = (size_t)(2 * E + 1) * sizeof(int);
+    agv_launch(moe_plan_kernel, 1u, 1024, smem, stream, ids, wts, T, top, E, GM, tok, dst, wpos,
+               pos_of, tile_e, agv_moe_plan_rows(T, top, E), agv_moe_plan_tiles(T, top, E));
+    AGV_LAUNCH_OK("moe_plan_kernel");
+    return 0;
+}
+
+// The grouped product over a plan.  a: rows of stride lda (a_index null: row = sorted
+// position); w (and w2 for the gated form): [E, N, K] dense; c: rows of stride ldc at
+// c_index[pos] (null: pos), times c_scale[pos] (null: 1).  in_dtype: a and the weights;
+// out_dtype: c.
+AGV_API int agv_moe_grouped(const void* a, long long lda, const int* a_index, const int* tok,
+                            const void* w, const void* w2, void* c, long long ldc,
+                            const int* c_index, const float* c_scale, const int* tile_e,
+                            int n_tiles, int N, int K, int in_dtype, int out_dtype, int act,
+                            cudaStream_t stream) {
+    AGV_REQUIRE(n_tiles >= 0 && N > 0 && K > 0, "moe_grouped: bad sizes");
+    AGV_REQUIRE(lda >= K && ldc >= N, "moe_grouped: row strides shorter than rows");
+    AGV_REQUIRE(n_tiles <= 65535, "moe_grouped: %d tiles exceed the grid limit", n_tiles);
+    if (n_tiles == 0) return 0;
+    dim3 grid((N + GN - 1) / GN, n_tiles);
+#define AGV_MOE(TA, TO)                                                                          \
+    do {                                                                                         \
+        if (w2)                                                                                  \
+            agv_launch(moe_grouped_kernel<TA, TA, TO, true>, grid, 256, 0, stream, (const TA*)a, \
+                       lda, a_index, tok, (const TA*)w, (const TA*)w2, (TO*)c, ldc, c_index,     \
+                       c_scale, tile_e, N, K, act);                                              \
+        else                                                                                     \
+            agv_launch(moe_grouped_kernel<TA, TA, TO, false>, grid, 256, 0, stream,              \
+                       (const TA*)a, lda, a_index, tok, (const TA*)w, (const TA*)nullptr,        \
+                       (TO*)c, ldc, c_index, c_scale, tile_e, N, K, act);                        \
+    } while (0)
+    if (in_dtype == AGV_F32 && out_dtype == AGV_F32) AGV_MOE(float, float);
+    else if (in_dtype == AGV_BF16 && out_dtype == AGV_BF16) AGV_MOE(__nv_bfloat16, __nv_bfloat16);
+    else if (in_dtype == AGV_BF16 && out_dtype == AGV_F32) AGV_MOE(__nv_bfloat16, float);
+    else return agv_fail(-1, "moe_grouped: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
+#undef AGV_MOE
+    AGV_LAUNCH_OK("moe_grouped_kernel");
+    return 0;
+}

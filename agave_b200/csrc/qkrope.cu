@@ -9,9 +9,23 @@
 // Cache addressing: position p of a sequence lives in ring row p % cap of its
 // slot; the row's page comes from the slot's page table.  A token whose row a
 // later token of the same step overwrites (p < len_after - cap) is not stored.
+//
+// Options: a value head size hdv that differs from the q / k head size hd (the row is
+// then q | k | v = nh * hd + nkv * hd + nkv * hdv wide), no kv heads at all (a layer that
+// attends to another layer's keys and values brings only queries), and a query
+// temperature: every q head is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1) at
+// position p, in 32-bit, before it is rounded.
 #include "common.cuh"
 #include "cache_write.cuh"
 #include <type_traits>
+
+struct QueryTemp {
+    float coef;                // 0: no temperature
+    int every;
+};
+__device__ __forceinline__ float query_temp(const QueryTemp& qt, int p) {
+    return 1.0f + qt.coef * logf((float)((p + 1) / qt.every + 1));
+}
 
 constexpr int QK_WARPS = 4;
 constexpr int QK_MAX_HD = 1024;
@@ -28,7 +42,8 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride,
                           int hd, const float* __restrict__ wq, const float* __restrict__ wk,
                           float eps, const float* __restrict__ cosv,
                           const float* __restrict__ sinv, int rotary_half,
-                          const int* __restrict__ positions, CacheWrite cw) {
+                          const int* __restrict__ positions, CacheWrite cw, int hdv_,
+                          QueryTemp qt) {
     pdl_wait();
     pdl_launch_next();
     extern __shared__ float smem[];
@@ -37,9 +52,14 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride,
     const long long item = (long long)blockIdx.x * QK_WARPS + warp;
     if (item >= (long long)n_tokens * heads) return;
     const int t = (int)(item / heads), head = (int)(item % heads);
-    float* buf = smem + warp * hd;
-    T* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
+    float* buf = smem + warp * max(hd, hdv_);
     const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
+    // where the head starts in the row, and how long it is (a v head may differ)
+    const int width = nh * hd + nkv * hd + nkv * hdv_;
+    const size_t head_at = (is_q || is_k) ? (size_t)head * hd
+                                          : (size_t)(nh + nkv) * hd + (size_t)(head - nh - nkv) * hdv_;
+    if (!is_q && !is_k) hd = hdv_;
+    T* src = qkv + (size_t)t * row_stride + head_at;
     const float* w = is_q ? wq : (is_k ? wk : nullptr);
     // where the row goes in the cache: these loads depend on one another, so they
     // start now and overlap the arithmetic below
@@ -57,7 +77,7 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride,
     float ss = 0.f;
     if (part) {
         // the projection arrives as 32-bit partial sums over ranges of K
-        const float* ps = part + (size_t)t * (size_t)(heads * hd) + (size_t)head * hd;
+        const float* ps = part + (size_t)t * (size_t)width + head_at;
         // eight elements per lane at a time, all their loads independent; the
         // ranges of K are added in order
         for (int e0 = 0; e0 < hd; e0 += 256) {
@@ -98,6 +118,10 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride,
             ss = warp_sum(ss);
             const float r = 1.0f / sqrtf(ss / (float)hd + eps);
             for (int e = lane; e < hd; e += 32) buf[e] = buf[e] * r * w[e];
+        }
+        if (is_q && qt.coef != 0.f) {
+            const float tau = query_temp(qt, positions[t]);
+            for (int e = lane; e < hd; e += 32) buf[e] *= tau;
         }
         __syncwarp();
         if (cosv) {
@@ -192,7 +216,7 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
                               const float* __restrict__ wq, const float* __restrict__ wk, float eps,
                               const float* __restrict__ cosv, const float* __restrict__ sinv,
                               const int* __restrict__ positions, CacheWrite cw, VtWrite vw,
-                              int vt_blocks) {
+                              int vt_blocks, QueryTemp qt) {
     // What the host copied in at the start of the step (positions, sequence index, slots,
     // lengths, page table) and the norm weights are read before the wait for the
     // predecessor, which only produces the projection (and, early in a step, cos / sin).
@@ -307,6 +331,7 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
         if (c_slot >= 0)
             c_page = cw.page_table[(size_t)c_slot * cw.max_pages + (c_pos % cw.cap) / cw.page];
     }
+    const float tau = (is_q && qt.coef != 0.f) ? query_temp(qt, positions[t]) : 1.f;
     // operands of the arithmetic: v[0..HALF) first run, v[HALF..NE) second run
     float wv[NE], cs[HALF], sn[HALF], v[NE];
     if (w) {
@@ -363,6 +388,10 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
 #pragma unroll
             for (int i = 0; i < NE; ++i) v[i] = v[i] * r * wv[i];
         }
+        if (is_q && qt.coef != 0.f) {
+#pragma unroll
+            for (int i = 0; i < NE; ++i) v[i] *= tau;
+        }
         if (rotate) {
 #pragma unroll
             for (int i = 0; i < HALF; ++i) {
@@ -392,8 +421,9 @@ static bool launch_qk_reg(T* qkv, long long row_stride, const float* part, int n
                           const float* wq, const float* wk, float eps, const float* cosv,
                           const float* sinv, int rotary_dim, const int* positions,
                           const CacheWrite& cw, const VtWrite& vw, unsigned main_blocks,
-                          cudaStream_t stream) {
-    if (hd % 64 != 0 || hd > 256 || (cosv && rotary_dim != hd)) return false;
+                          cudaStream_t stream, int hdv, QueryTemp qt) {
+    if (hd % 64 != 0 || hd > 256 || (cosv && rotary_dim != hd) || (hdv != hd && nkv > 0))
+        return false;
     if (vw.vt && !std::is_same<T, __nv_bfloat16>::value) return false;
     const unsigned vt_blocks =
         vw.vt ? (unsigned)((n_tokens + 63) / 64) * (unsigned)(nkv * hd / 64) : 0u;
@@ -407,11 +437,11 @@ static bool launch_qk_reg(T* qkv, long long row_stride, const float* part, int n
     if (part && n_splits > 1)                                                                   \
         agv_launch(qk_norm_rope_store_reg_kernel<T, NE, true>, grid, QK_WARPS * 32, 0, stream,  \
                    qkv, row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, wq, wk,    \
-                   eps, cosv, sinv, positions, cw, vw, (int)vt_blocks);                         \
+                   eps, cosv, sinv, positions, cw, vw, (int)vt_blocks, qt);                     \
     else                                                                                        \
         agv_launch(qk_norm_rope_store_reg_kernel<T, NE, false>, grid, QK_WARPS * 32, 0, stream, \
                    qkv, row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, wq, wk,    \
-                   eps, cosv, sinv, positions, cw, vw, (int)vt_blocks)
+                   eps, cosv, sinv, positions, cw, vw, (int)vt_blocks, qt)
     if (hd == 64) { AGV_QK_REG(2); }
     else if (hd == 128) { AGV_QK_REG(4); }
     else if (hd == 192) { AGV_QK_REG(6); }
@@ -428,20 +458,30 @@ static bool launch_qk_reg(T* qkv, long long row_stride, const float* part, int n
 // With vt != null (bfloat16 only) the values are also written transposed into
 // vt [nkv * hd, vt_ld] (see VtWrite); that needs seq_index, positions, cu_seqlens
 // [n_seq + 1] and the greatest sequence length.
-AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, const float* part,
-                                   int n_splits, int n_tokens, int nh,
-                                   int nkv, int hd, const float* wq, const float* wk, float eps,
-                                   const float* cosv, const float* sinv, int rotary_dim,
-                                   const int* positions, void* k_pool, void* v_pool,
-                                   const int* page_table, const int* slots, const int* lens,
-                                   const int* seq_index, int max_pages, int page, int cap,
-                                   void* vt, long long vt_ld, const int* cu_seqlens, int n_seq,
-                                   int max_len, cudaStream_t stream) {
-    AGV_REQUIRE(n_tokens >= 0 && nh > 0 && nkv > 0 && hd > 0, "qk_norm_rope: bad sizes");
-    AGV_REQUIRE(hd <= QK_MAX_HD, "qk_norm_rope: head_dim %d exceeds %d", hd, QK_MAX_HD);
+// hdv: the value head size (the row is q | k | v with v heads of hdv; the value pool's rows
+// are nkv * hdv); nkv may be 0 (queries only).  qt_coef != 0: the query temperature
+// 1 + qt_coef * ln(floor((p + 1) / qt_every) + 1) multiplies every q head (needs positions).
+AGV_API int agv_qk_norm_rope_store_ex(void* qkv, int dtype, long long row_stride, const float* part,
+                                      int n_splits, int n_tokens, int nh,
+                                      int nkv, int hd, const float* wq, const float* wk, float eps,
+                                      const float* cosv, const float* sinv, int rotary_dim,
+                                      const int* positions, void* k_pool, void* v_pool,
+                                      const int* page_table, const int* slots, const int* lens,
+                                      const int* seq_index, int max_pages, int page, int cap,
+                                      void* vt, long long vt_ld, const int* cu_seqlens, int n_seq,
+                                      int max_len, int hdv, float qt_coef, int qt_every,
+                                      cudaStream_t stream) {
+    AGV_REQUIRE(n_tokens >= 0 && nh > 0 && nkv >= 0 && hd > 0 && hdv > 0, "qk_norm_rope: bad sizes");
+    AGV_REQUIRE(hd <= QK_MAX_HD && hdv <= QK_MAX_HD, "qk_norm_rope: head sizes %d, %d exceed %d",
+                hd, hdv, QK_MAX_HD);
+    AGV_REQUIRE(qt_coef == 0.f || (qt_every > 0 && positions),
+                "qk_norm_rope: the query temperature needs positions and a period >= 1");
+    AGV_REQUIRE(!vt || hdv == hd, "qk_norm_rope: the transposed values need equal head sizes");
+    AGV_REQUIRE(nkv > 0 || !k_pool, "qk_norm_rope: nothing to store without kv heads");
     AGV_REQUIRE(rotary_dim % 2 == 0 && rotary_dim <= hd, "qk_norm_rope: rotary_dim %d must be even "
                 "and at most head_dim %d", rotary_dim, hd);
-    AGV_REQUIRE(row_stride >= (long long)(nh + 2 * nkv) * hd, "qk_norm_rope: row stride too short");
+    const long long width = (long long)(nh + nkv) * hd + (long long)nkv * hdv;
+    AGV_REQUIRE(row_stride >= width, "qk_norm_rope: row stride too short");
     AGV_REQUIRE(!k_pool || (v_pool && page_table && slots && lens && seq_index && page > 0 &&
                             cap > 0 && max_pages > 0), "qk_norm_rope: incomplete cache arguments");
     AGV_REQUIRE(!cosv || (sinv && positions), "qk_norm_rope: cos without sin or positions");
@@ -453,32 +493,33 @@ AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, c
                 "cu_seqlens");
     if (n_tokens == 0) return 0;
     VtWrite vw{(__nv_bfloat16*)vt, vt_ld, cu_seqlens, seq_index};
-    const long long split_stride = (long long)n_tokens * (nh + 2 * nkv) * hd;
+    const long long split_stride = (long long)n_tokens * width;
+    const QueryTemp qt{qt_coef, qt_every > 0 ? qt_every : 1};
     CacheWrite cw{k_pool, v_pool, page_table, slots, lens, seq_index, max_pages, page, cap};
     const long long items = (long long)n_tokens * (nh + 2 * nkv);
     const unsigned grid = (unsigned)((items + QK_WARPS - 1) / QK_WARPS);
-    const size_t smem = (size_t)QK_WARPS * hd * sizeof(float);
+    const size_t smem = (size_t)QK_WARPS * (hd > hdv ? hd : hdv) * sizeof(float);
     const int half = cosv ? rotary_dim / 2 : 0;
     if (dtype == AGV_F32 &&
         launch_qk_reg<float>((float*)qkv, row_stride, part, n_splits, split_stride, n_tokens, nh,
                              nkv, hd, wq, wk, eps, cosv, sinv, rotary_dim, positions, cw, vw, grid,
-                             stream)) {
+                             stream, hdv, qt)) {
         AGV_LAUNCH_OK("qk_norm_rope_store_reg_kernel");
         return 0;
     }
     if (dtype == AGV_BF16 &&
         launch_qk_reg<__nv_bfloat16>((__nv_bfloat16*)qkv, row_stride, part, n_splits, split_stride,
                                      n_tokens, nh, nkv, hd, wq, wk, eps, cosv, sinv, rotary_dim,
-                                     positions, cw, vw, grid, stream)) {
+                                     positions, cw, vw, grid, stream, hdv, qt)) {
         AGV_LAUNCH_OK("qk_norm_rope_store_reg_kernel");
         return 0;
     }
     if (dtype == AGV_F32)
         agv_launch(qk_norm_rope_store_kernel<float>, grid, QK_WARPS * 32, smem, stream, (float*)qkv, row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, hd, wq, wk,
-            eps, cosv, sinv, half, positions, cw);
+            eps, cosv, sinv, half, positions, cw, hdv, qt);
     else if (dtype == AGV_BF16)
         agv_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, QK_WARPS * 32, smem, stream, (__nv_bfloat16*)qkv, row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, hd,
-            wq, wk, eps, cosv, sinv, half, positions, cw);
+            wq, wk, eps, cosv, sinv, half, positions, cw, hdv, qt);
     else
         return agv_fail(-1, "qk_norm_rope: unknown dtype %d", dtype);
     AGV_LAUNCH_OK("qk_norm_rope_store_kernel");
@@ -490,4 +531,20 @@ AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, c
                                     stream);
     }
     return 0;
+}
+
+AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, const float* part,
+                                   int n_splits, int n_tokens, int nh,
+                                   int nkv, int hd, const float* wq, const float* wk, float eps,
+                                   const float* cosv, const float* sinv, int rotary_dim,
+                                   const int* positions, void* k_pool, void* v_pool,
+                                   const int* page_table, const int* slots, const int* lens,
+                                   const int* seq_index, int max_pages, int page, int cap,
+                                   void* vt, long long vt_ld, const int* cu_seqlens, int n_seq,
+                                   int max_len, cudaStream_t stream) {
+    AGV_REQUIRE(nkv > 0, "qk_norm_rope: bad sizes");
+    return agv_qk_norm_rope_store_ex(qkv, dtype, row_stride, part, n_splits, n_tokens, nh, nkv, hd,
+                                     wq, wk, eps, cosv, sinv, rotary_dim, positions, k_pool, v_pool,
+                                     page_table, slots, lens, seq_index, max_pages, page, cap, vt,
+                                     vt_ld, cu_seqlens, n_seq, max_len, hd, 0.f, 1, stream);
 }

@@ -192,6 +192,129 @@ def norm_residual(h: Optional[torch.Tensor], y: Optional[torch.Tensor],
             ctypes.c_float(eps_next), 1 if (add_residual and y is not None) else 0, _stream()))
 
 
+def layer_norm_join(h: Optional[torch.Tensor], y: Optional[torch.Tensor],
+                    w_post: Optional[torch.Tensor], b_post: Optional[torch.Tensor],
+                    w_next: Optional[torch.Tensor], b_next: Optional[torch.Tensor],
+                    x: Optional[torch.Tensor], eps_post: float = 0.0, eps_next: float = 0.0,
+                    mult: float = 1.0, rows: Optional[torch.Tensor] = None,
+                    add_residual: bool = True, rms: bool = False) -> None:
+    """The layer-norm family in one launch (mean and variance, weight and bias).
+
+    y None:  x = N(h[rows]; w_next, b_next)               (rows optional)
+    else:    b = y (summed over a leading split axis if y is 3-D);
+             b = N(b; w_post, b_post) if w_post; b *= mult; h += b if add_residual;
+             x = N(h or b; w_next, b_next) if w_next, else x = b if x is given.
+    h is the 32-bit residual stream [R, H]; weights and biases are 32-bit.  ``rms``: the
+    mean is not taken off (an RMS norm with an optional bias and the multiplier)."""
+    for t, n in ((h, "h"), (w_post, "w_post"), (b_post, "b_post"), (w_next, "w_next"),
+                 (b_next, "b_next")):
+        _f32(t, n)
+    _i32(rows, "rows")
+    n_splits, split_stride, y_code = 1, 0, F32
+    if y is not None:
+        _dense(y, "y")
+        y_code = dtype_code(y.dtype)
+        if y.dim() == 3:
+            n_splits, R, H = y.shape
+            split_stride = R * H
+        else:
+            R, H = y.shape
+    else:
+        H = h.shape[-1]
+        R = rows.numel() if rows is not None else h.shape[0]
+    if h is not None:
+        _dense(h, "h")
+    x_code = F32
+    if x is not None:
+        _dense(x, "x")
+        x_code = dtype_code(x.dtype)
+        assert x.shape == (R, H), (x.shape, R, H)
+    with _span("norm", _nbytes(y, x) + (R * H * 4 * (2 if y is not None and add_residual else 1)
+                                         if h is not None else 0)):
+        _check(library().agv_layer_norm_join(
+            _ptr(h), _ptr(y), y_code, n_splits, ctypes.c_longlong(split_stride), _ptr(w_post),
+            _ptr(b_post), _ptr(w_next), _ptr(b_next), _ptr(x), x_code, _ptr(rows), R, H,
+            ctypes.c_float(eps_post), ctypes.c_float(eps_next), ctypes.c_float(mult),
+            1 if (add_residual and y is not None) else 0, 1 if rms else 0, _stream()))
+
+
+def soft_cap(z: torch.Tensor, cap: float) -> None:
+    """z <- cap * tanh(z / cap) in place (32-bit logits)."""
+    _f32(z, "z"); _dense(z, "z")
+    with _span("soft_cap", 2 * _nbytes(z)):
+        _check(library().agv_soft_cap(_ptr(z), ctypes.c_longlong(z.numel()), ctypes.c_float(cap),
+                                      _stream()))
+
+
+# ------------------------------------------------------ routed feed-forward
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor],
+              n_groups: int, keep: int, top: int, ids: torch.Tensor, wts: torch.Tensor) -> None:
+    """ids, wts [T, top]: the experts each token of x [T, H] uses and their weights.
+    s = sigmoid(W_r x) in 32-bit; s + correction chooses (only among the experts of the
+    ``keep`` groups, of ``n_groups`` equal ones, whose two largest choice scores sum highest),
+    s itself weighs."""
+    T, H = x.shape
+    E = w_router.shape[0]
+    assert w_router.shape == (E, H) and x.stride(1) == 1 and x.dtype == w_router.dtype
+    _dense(w_router, "w_router"); _f32(correction, "correction"); _i32(ids, "ids"); _f32(wts, "wts")
+    _dense(ids, "ids"); _dense(wts, "wts")
+    assert ids.shape == (T, top) and wts.shape == (T, top)
+    with _span("router", _nbytes(x, w_router), 2 * T * E * H):
+        _check(library().agv_moe_route(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(w_router),
+                                       _ptr(correction), dtype_code(x.dtype), T, H, E, n_groups,
+                                       keep, top, _ptr(ids), _ptr(wts), _stream()))
+
+
+class MoePlan:
+    """Where the (token, choice) pairs of a step lie once sorted by expert (device arrays;
+    see ``csrc/moe.cu``)."""
+    __slots__ = ("T", "top", "E", "rows", "tiles", "tok", "dst", "wpos", "pos_of", "tile_e")
+
+
+def moe_plan(ids: torch.Tensor, wts: torch.Tensor, n_experts: int) -> MoePlan:
+    T, top = ids.shape
+    lib = library()
+    p = MoePlan()
+    p.T, p.top, p.E = T, top, n_experts
+    p.rows = lib.agv_moe_plan_rows(T, top, n_experts)
+    p.tiles = lib.agv_moe_plan_tiles(T, top, n_experts)
+    dev = ids.device
+    ints = torch.empty(2 * p.rows + T * top + p.tiles, dtype=torch.int32, device=dev)
+    p.tok, p.dst = ints[:p.rows], ints[p.rows:2 * p.rows]
+    p.pos_of = ints[2 * p.rows:2 * p.rows + T * top]
+    p.tile_e = ints[2 * p.rows + T * top:]
+    p.wpos = torch.empty(p.rows, dtype=torch.float32, device=dev)
+    _check(lib.agv_moe_plan(_ptr(ids), _ptr(wts), T, top, n_experts, _ptr(p.tok), _ptr(p.dst),
+                            _ptr(p.wpos), _ptr(p.pos_of), _ptr(p.tile_e), _stream()))
+    return p
+
+
+def moe_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: MoePlan,
+                w2: Optional[torch.Tensor] = None, activation: str = "silu",
+                gather: bool = False, scatter: bool = False, op: str = "experts") -> None:
+    """The experts' product over a plan: out[pos] = a[row(pos)] w[e(pos)]^T, or with w2 the
+    gated pair.  w, w2: [E, N, K].  ``gather``: a's rows are tokens (row = the pair's token),
+    else sorted positions.  ``scatter``: out is [top * T, N] and a pair's row, times its
+    weight, goes to [choice * T + token]; else out's rows are sorted positions."""
+    E, N, K = w.shape
+    _dense(w, "w")
+    assert a.stride(1) == 1 and out.stride(1) == 1 and a.shape[1] == K and out.shape[1] == N
+    assert a.dtype == w.dtype
+    if w2 is not None:
+        _dense(w2, "w2")
+        assert w2.shape == w.shape and w2.dtype == w.dtype
+    pairs = plan.T * plan.top
+    n = 2 if w2 is not None else 1
+    with _span(op, n * min(E, pairs) * N * K * w.element_size() + pairs * (K + N) * a.element_size(),
+               2 * n * pairs * N * K):
+        _check(library().agv_moe_grouped(
+            _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(plan.tok) if gather else None,
+            _ptr(plan.tok), _ptr(w), _ptr(w2), _ptr(out), ctypes.c_longlong(out.stride(0)),
+            _ptr(plan.dst) if scatter else None, _ptr(plan.wpos) if scatter else None,
+            _ptr(plan.tile_e), plan.tiles, N, K, dtype_code(a.dtype), dtype_code(out.dtype),
+            ACT[activation], _stream()))
+
+
 # ------------------------------------------------------------ matrix products
 def _linear_cost(x, w, w2, out):
     """(bytes, flops) of a projection: weights and operands once, 2 T N K flops."""
@@ -234,19 +357,24 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
                        seq_index: Optional[torch.Tensor] = None, page: int = 0,
                        cap: int = 0, partial: Optional[torch.Tensor] = None,
                        vt: Optional[torch.Tensor] = None, cu_seqlens: Optional[torch.Tensor] = None,
-                       max_len: int = 0) -> None:
+                       max_len: int = 0, value_dim: int = 0, q_temp=None) -> None:
     """In place on qkv [T, (nh + 2 nkv) * hd]: per-head norm of q and k, rotation,
     and (if pools are given) the store of k and v rows into the paged cache.
     ``partial`` [S, T, (nh + 2 nkv) * hd] (32-bit partial sums of the projection)
     replaces qkv as the input; qkv then only receives the result.  ``vt`` (from
     ``prefill_values_scratch``) also receives the values transposed, for the prompt
-    attention; that needs seq_index, positions, cu_seqlens and the greatest length."""
+    attention; that needs seq_index, positions, cu_seqlens and the greatest length.
+    ``value_dim``: the size of a v head where it differs from head_dim (the row is then
+    nh * hd + nkv * hd + nkv * value_dim wide); n_kv_heads may be 0 (queries alone).
+    ``q_temp`` = (coef, every): every q head is multiplied by
+    1 + coef * ln(floor((p + 1) / every) + 1) at position p."""
     T = qkv.shape[0]
     n_splits = 0
+    hdv = value_dim or head_dim
     if partial is not None:
         _f32(partial, "partial"); _dense(partial, "partial")
         assert partial.dim() == 3 and partial.shape[1] == T
-        assert partial.shape[2] == (n_heads + 2 * n_kv_heads) * head_dim
+        assert partial.shape[2] == (n_heads + n_kv_heads) * head_dim + n_kv_heads * hdv
         n_splits = partial.shape[0]
     assert qkv.stride(1) == 1
     _f32(wq, "wq"); _f32(wk, "wk"); _f32(cos, "cos"); _f32(sin, "sin")
@@ -263,13 +391,14 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
         assert vt.dtype == torch.bfloat16 and vt.shape[0] == n_kv_heads * head_dim
         n_seq = cu_seqlens.numel() - 1
     with _span("qk_norm_rope", 2 * _nbytes(qkv) + _nbytes(partial, vt)):
-        _check(library().agv_qk_norm_rope_store(
+        coef, every = q_temp if q_temp is not None else (0.0, 1)
+        _check(library().agv_qk_norm_rope_store_ex(
             _ptr(qkv), dtype_code(qkv.dtype), ctypes.c_longlong(qkv.stride(0)), _ptr(partial),
             n_splits, T, n_heads, n_kv_heads, head_dim, _ptr(wq), _ptr(wk), ctypes.c_float(eps),
             _ptr(cos), _ptr(sin), rotary_dim, _ptr(positions), _ptr(k_pool), _ptr(v_pool),
             _ptr(page_table), _ptr(slots), _ptr(lens), _ptr(seq_index), max_pages, page, cap,
             _ptr(vt), ctypes.c_longlong(vt.shape[1] if vt is not None else 0), _ptr(cu_seqlens),
-            n_seq, max_len, _stream()))
+            n_seq, max_len, hdv, ctypes.c_float(coef), int(every), _stream()))
 
 
 _FUSED_QKV = os.environ.get("AGAVE_B200_FUSED_QKV_PREFILL", "1") != "0"
@@ -338,38 +467,43 @@ def qkv_prefill(x: torch.Tensor, w: torch.Tensor, qkv: torch.Tensor, n_heads: in
 def attention_prefill_simt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
                            positions: torch.Tensor, seq_index: torch.Tensor,
                            cu_seqlens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
-                           scale: float, window: int) -> None:
-    """Prompts that start at 0; q [T, nh*hd], k, v [T, nkv*hd] row-strided views."""
+                           scale: float, window: int, value_dim: int = 0,
+                           sinks: Optional[torch.Tensor] = None) -> None:
+    """Prompts that start at 0; q [T, nh*hd], k [T, nkv*hd], v [T, nkv*hdv] row-strided
+    views (hdv = value_dim or head_dim), out [T, nh*hdv]; ``sinks`` [nh]: a logit per query
+    head that joins its softmax denominator once."""
     T = q.shape[0]
     assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1
-    assert k.stride(0) == v.stride(0)
-    _dense(out, "out")
+    _dense(out, "out"); _f32(sinks, "sinks")
     _i32(positions, "positions"); _i32(seq_index, "seq_index"); _i32(cu_seqlens, "cu_seqlens")
-    _check(library().agv_attention_prefill_simt(
+    _check(library().agv_attention_prefill_simt_ex(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), _ptr(v),
         ctypes.c_longlong(k.stride(0)), _ptr(out), dtype_code(q.dtype), _ptr(positions),
         _ptr(seq_index), _ptr(cu_seqlens), T, n_heads, n_kv_heads, head_dim,
-        ctypes.c_float(scale), window, _stream()))
+        ctypes.c_float(scale), window, value_dim or head_dim, ctypes.c_longlong(v.stride(0)),
+        _ptr(sinks), _stream()))
 
 
 def attention_paged_simt(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor,
                          v_pool: torch.Tensor, page_table: torch.Tensor, slots: torch.Tensor,
                          positions: torch.Tensor, seq_index: torch.Tensor, page: int, cap: int,
                          n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                         window: int) -> None:
+                         window: int, value_dim: int = 0,
+                         sinks: Optional[torch.Tensor] = None) -> None:
     """Queries against the paged cache; their own keys are already stored."""
     T = q.shape[0]
     assert q.stride(1) == 1
+    _f32(sinks, "sinks")
     _dense(out, "out"); _dense(k_pool, "k_pool"); _dense(v_pool, "v_pool")
     for t, n in ((positions, "positions"), (page_table, "page_table"), (slots, "slots"),
                  (seq_index, "seq_index")):
         _i32(t, n)
     assert k_pool.dtype == q.dtype
-    _check(library().agv_attention_paged_simt(
+    _check(library().agv_attention_paged_simt_ex(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(out), dtype_code(q.dtype), _ptr(k_pool),
         _ptr(v_pool), _ptr(page_table), _ptr(slots), _ptr(positions), _ptr(seq_index),
         page_table.shape[1], page, cap, T, n_heads, n_kv_heads, head_dim,
-        ctypes.c_float(scale), window, _stream()))
+        ctypes.c_float(scale), window, value_dim or head_dim, _ptr(sinks), _stream()))
 
 
 # ------------------------------------------------------------------- sampling
@@ -693,17 +827,20 @@ def gemv_few(w: torch.Tensor, out: torch.Tensor, x: Optional[torch.Tensor] = Non
 
 def attention_prefill_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
                           cu_seqlens: torch.Tensor, max_len: int, n_heads: int, n_kv_heads: int,
-                          head_dim: int, scale: float, window: int) -> None:
+                          head_dim: int, scale: float, window: int,
+                          sinks: Optional[torch.Tensor] = None) -> None:
     """Prompts that start at 0 on the tensor cores (bfloat16, head sizes in steps
     of 8 up to 256); q, k, v are row-strided views, out is dense."""
+    _f32(sinks, "sinks")
     assert q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype
     assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1
     assert k.stride(0) == v.stride(0)
     _dense(out, "out"); _i32(cu_seqlens, "cu_seqlens")
-    _check(library().agv_attention_prefill_mma(
+    _check(library().agv_attention_prefill_mma_ex(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), _ptr(v),
         ctypes.c_longlong(k.stride(0)), _ptr(out), _ptr(cu_seqlens), cu_seqlens.numel() - 1,
-        max_len, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window, _stream()))
+        max_len, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window, _ptr(sinks),
+        _stream()))
 
 
 def prefill_values_scratch(T: int, B: int, n_kv_heads: int, head_dim: int,
@@ -728,7 +865,8 @@ def transpose_values(v: torch.Tensor, vt: torch.Tensor, cu_seqlens: torch.Tensor
 def attention_prefill_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
                          cu_seqlens: torch.Tensor, max_len: int, n_heads: int, n_kv_heads: int,
                          head_dim: int, scale: float, window: int,
-                         vt: Optional[torch.Tensor] = None) -> None:
+                         vt: Optional[torch.Tensor] = None,
+                         sinks: Optional[torch.Tensor] = None) -> None:
     """Prompts that start at 0 on the tcgen05 tensor cores (bfloat16, head sizes in
     steps of 16 up to 256); q, k, v are row-strided views, out is dense.  ``vt``:
     the values already transposed (by ``qk_norm_rope_store``); else this call
@@ -742,11 +880,12 @@ def attention_prefill_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out:
     if vt is None:
         vt = prefill_values_scratch(T, B, n_kv_heads, head_dim, q.device)
     _dense(vt, "vt")
-    _check(library().agv_attention_prefill_tc(
+    _f32(sinks, "sinks")
+    _check(library().agv_attention_prefill_tc_ex(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), _ptr(v),
         ctypes.c_longlong(k.stride(0)), _ptr(out), _ptr(vt), ctypes.c_longlong(vt.shape[1]),
         1 if ready else 0, _ptr(cu_seqlens), B, T, max_len, n_heads, n_kv_heads, head_dim,
-        ctypes.c_float(scale), window, _stream()))
+        ctypes.c_float(scale), window, _ptr(sinks), _stream()))
 
 
 def attention_tc_status() -> int:
@@ -763,32 +902,38 @@ def attention_tc_status() -> int:
 PREFILL_TC_MIN_TOKENS = 192
 
 
-def attention_prefill_wants_transposed_values(qkv: torch.Tensor, head_dim: int) -> bool:
+def attention_prefill_wants_transposed_values(qkv: torch.Tensor, head_dim: int,
+                                              value_dim: int = 0) -> bool:
     """Whether ``attention_prefill`` on views of this projection output will take the
     tcgen05 kernel, which reads the values transposed."""
-    return (_PREFILL_TC and qkv.shape[0] > PREFILL_TC_MIN_TOKENS and qkv.dtype == torch.bfloat16 and
+    return ((value_dim or head_dim) == head_dim and _PREFILL_TC and qkv.shape[0] > PREFILL_TC_MIN_TOKENS and qkv.dtype == torch.bfloat16 and
             head_dim % 16 == 0 and head_dim <= 256 and qkv.stride(0) % 8 == 0 and
             qkv.data_ptr() % 16 == 0)
 
 
 def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, window,
-                      vt=None) -> None:
+                      vt=None, value_dim: int = 0, sinks=None) -> None:
     """Prompt attention of one layer in bfloat16: the tcgen05 kernel for head sizes
     in steps of 16 up to 256, the mma.sync kernel for the other multiples of 8; else
-    the one-warp-per-(token, head) kernel."""
-    aligned = (q.dtype == torch.bfloat16 and head_dim <= 256 and
+    (and for value heads of another size than the keys') the one-warp-per-(token, head)
+    kernel.  ``sinks`` [nh]: a logit per query head that joins its denominator once."""
+    hdv = value_dim or head_dim
+    aligned = (q.dtype == torch.bfloat16 and head_dim <= 256 and hdv == head_dim and
+               k.stride(0) == v.stride(0) and
                q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and
                k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0)
     with _span("attention", *_attention_cost(ctx, q, k, v, out, n_heads, head_dim, window)):
-        if aligned and head_dim % 16 == 0 and _PREFILL_TC and q.shape[0] > PREFILL_TC_MIN_TOKENS:
+        if (aligned and head_dim % 16 == 0 and _PREFILL_TC and scale > 0 and
+                q.shape[0] > PREFILL_TC_MIN_TOKENS):
             attention_prefill_tc(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads, n_kv_heads,
-                                 head_dim, scale, window, vt=vt)
+                                 head_dim, scale, window, vt=vt, sinks=sinks)
         elif aligned and head_dim % 8 == 0:
             attention_prefill_mma(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads,
-                                  n_kv_heads, head_dim, scale, window)
+                                  n_kv_heads, head_dim, scale, window, sinks=sinks)
         else:
             attention_prefill_simt(q, k, v, out, ctx.positions, ctx.seq_index, ctx.cu_seqlens,
-                                   n_heads, n_kv_heads, head_dim, scale, window)
+                                   n_heads, n_kv_heads, head_dim, scale, window, value_dim=hdv,
+                                   sinks=sinks)
 
 
 def _attention_cost(ctx, q, k, v, out, n_heads, head_dim, window, n_kv_heads=0):
@@ -867,7 +1012,8 @@ def attention_decode_split(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Ten
                            positions: torch.Tensor, page: int, cap: int, n_heads: int,
                            n_kv_heads: int, head_dim: int, scale: float, window: int,
                            max_keys: int, part_acc: Optional[torch.Tensor] = None,
-                           part_ml: Optional[torch.Tensor] = None) -> None:
+                           part_ml: Optional[torch.Tensor] = None,
+                           sinks: Optional[torch.Tensor] = None) -> None:
     """One query per batch entry against the paged cache, keys split into chunks
     whose partial results go through scratch memory (allocated here if not given)."""
     B = q.shape[0]
@@ -885,11 +1031,12 @@ def attention_decode_split(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Ten
     assert part_ml.numel() >= B * n_heads * n_splits * 2
     _f32(part_acc, "part_acc"); _f32(part_ml, "part_ml")
     counters = _decode_counters(q.device, B * n_heads)
-    _check(library().agv_attention_decode(
+    _f32(sinks, "sinks")
+    _check(library().agv_attention_decode_ex(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(out), dtype_code(q.dtype), _ptr(k_pool),
         _ptr(v_pool), _ptr(page_table), _ptr(slots), _ptr(positions), page_table.shape[1], page,
         cap, B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window, max_keys,
-        _ptr(part_acc), _ptr(part_ml), _ptr(counters), _stream()))
+        _ptr(part_acc), _ptr(part_ml), _ptr(counters), _ptr(sinks), _stream()))
 
 
 _FUSED_DECODE = os.environ.get("AGAVE_B200_FUSED_DECODE_ATTENTION", "1") != "0"
@@ -905,14 +1052,19 @@ def attention_decode_fused(partial: torch.Tensor, wq: Optional[torch.Tensor],
                            wk: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
                            sin: Optional[torch.Tensor], store_kv: bool, out: torch.Tensor, view,
                            ctx, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                           window: int) -> None:
+                           window: int, sinks: Optional[torch.Tensor] = None, q_temp=None,
+                           q_only: bool = False) -> None:
     """Decode attention of one layer with the q/k norm, the rotation and the cache store
     of the new position inside the attention kernel: ``partial`` [G, B, (nh + 2 nkv) *
-    hd] are the projection's 32-bit partial sums."""
+    hd] are the projection's 32-bit partial sums ([G, B, nh * hd] with ``q_only``: a layer
+    that attends to keys and values another layer stored).  ``sinks`` [nh]: a logit per
+    query head joining its denominator once; ``q_temp`` = (coef, every): the query
+    temperature 1 + coef * ln(floor((p + 1) / every) + 1)."""
     _f32(partial, "partial"); _dense(partial, "partial"); _dense(out, "out")
-    _f32(wq, "wq"); _f32(wk, "wk"); _f32(cos, "cos"); _f32(sin, "sin")
+    _f32(wq, "wq"); _f32(wk, "wk"); _f32(cos, "cos"); _f32(sin, "sin"); _f32(sinks, "sinks")
     G, B, width = partial.shape
-    assert width == (n_heads + 2 * n_kv_heads) * head_dim and out.dtype == torch.bfloat16
+    assert width == (n_heads + (0 if q_only else 2 * n_kv_heads)) * head_dim
+    assert out.dtype == torch.bfloat16 and not (q_only and store_kv)
     assert view.k_pool.dtype == torch.bfloat16
     if cos is not None:
         _dense(cos, "cos"); _dense(sin, "sin")
@@ -928,26 +1080,31 @@ def attention_decode_fused(partial: torch.Tensor, wq: Optional[torch.Tensor],
     counters = _decode_counters(out.device, B * n_heads)
     with _span("attention", *_attention_cost(ctx, partial, None, None, out, n_heads, head_dim,
                                              window, n_kv_heads)):
-        _check(library().agv_attention_decode_fused(
+        coef, every = q_temp if q_temp is not None else (0.0, 1)
+        _check(library().agv_attention_decode_fused_ex(
             _ptr(partial), G, _ptr(wq), _ptr(wk), ctypes.c_float(eps), _ptr(cos), _ptr(sin),
             1 if store_kv else 0, _ptr(out), _ptr(view.k_pool), _ptr(view.v_pool),
             _ptr(view.page_table), _ptr(ctx.slots), _ptr(ctx.positions),
             view.page_table.shape[1], view.page, view.cap, B, n_heads, n_kv_heads, head_dim,
             ctypes.c_float(scale), window, max_keys, _ptr(part_acc), _ptr(part_ml),
-            _ptr(counters), _stream()))
+            _ptr(counters), _ptr(sinks), ctypes.c_float(coef), int(every), 1 if q_only else 0,
+            _stream()))
 
 
-def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, window) -> None:
+def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, window,
+                     value_dim: int = 0, sinks=None) -> None:
     """Decode attention of one layer: the split kernel for head sizes in steps of
-    16 up to 512, else the one-warp-per-head kernel."""
+    16 up to 512, else (and for value heads of another size than the keys') the
+    one-warp-per-head kernel."""
+    hdv = value_dim or head_dim
     with _span("attention", *_attention_cost(ctx, q, None, None, out, n_heads, head_dim, window,
                                              n_kv_heads)):
-        if head_dim % 16 == 0 and head_dim <= 512:
+        if head_dim % 16 == 0 and head_dim <= 512 and hdv == head_dim:
             max_keys = min(window, ctx.max_len) if window else ctx.max_len
             attention_decode_split(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
                                    ctx.positions, view.page, view.cap, n_heads, n_kv_heads,
-                                   head_dim, scale, window, max(1, max_keys))
+                                   head_dim, scale, window, max(1, max_keys), sinks=sinks)
         else:
             attention_paged_simt(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
                                  ctx.positions, ctx.seq_index, view.page, view.cap, n_heads,
-                                 n_kv_heads, head_dim, scale, window)
+                                 n_kv_heads, head_dim, scale, window, value_dim=hdv, sinks=sinks)

@@ -101,7 +101,8 @@ class DecoderModel:
             p = "stream_position."
             self.stream_position.load({k[len(p):]: v for k, v in tensors.items()
                                        if k.startswith(p)}, dev)
-        self.final_norm.load({"weight": tensors["final_norm.weight"]}, dev)
+        p = "final_norm."
+        self.final_norm.load({k[len(p):]: v for k, v in tensors.items() if k.startswith(p)}, dev)
         if self.spec.tie_embeddings:
             self.head = Linear(self.embed_table, role="lm_head")
         else:
@@ -242,7 +243,10 @@ class DecoderModel:
         self.final_norm.forward(h, x, rows=rows)
         if out is None:
             out = ctx.new(R, self.spec.vocab_size, dtype=torch.float32)
-        return self.head(x, out=out)
+        self.head(x, out=out)
+        if self.spec.logit_softcap is not None:
+            kernels.soft_cap(out, self.spec.logit_softcap)
+        return out
 
     def greedy_tokens(self, h: torch.Tensor, rows: torch.Tensor, ctx,
                       out: torch.Tensor) -> bool:
@@ -250,7 +254,8 @@ class DecoderModel:
         logits ever being written (the head product takes the arg max in its epilogue;
         the reference chooses in the same place, src/models/gemma3.zig:352-367).
         Returns False, having done nothing, where the head has no such kernel (32-bit
-        weights, more rows than it takes): the caller then asks for ``logits``."""
+        weights, more rows than it takes): the caller then asks for ``logits``.  A soft cap
+        of the logits is increasing, so it moves no arg max and is left out here."""
         x = ctx.new(rows.numel(), self.spec.hidden_size)
         if not kernels.linear_argmax_supported(x, self.head.weight):
             return False

@@ -82,7 +82,11 @@ def standard_blocks(model) -> bool:
                 return False
         if b.mixer.position is not None and type(b.mixer.position) is not RotaryEmbedding:
             return False
-    return type(model.final_norm) is RMSNorm
+        # options the C++ step function does not describe: a sink, a query temperature,
+        # value heads of their own size, a multiplier on the branches
+        if not getattr(b.mixer, "plain", True) or getattr(b, "mult", 1.0) != 1.0:
+            return False
+    return type(model.final_norm) is RMSNorm and model.spec.logit_softcap is None
 
 
 class NativeStep:

@@ -19,6 +19,13 @@ sizes allow, the decode attention kernel takes the projection's partial sums and
 the norm, the rotation and that store itself).  A call
 that does not write the cache reads what the owning call stored: during a
 prompt step through ``ctx.step_kv``, during decoding through the cache.
+
+Options of the spec, each a parameter of the kernels: value heads of another size
+than the keys' (``value_dim``), a sink logit per query head that joins the softmax
+denominator once (``sink``; tensor ``sink``), a query temperature that multiplies q by
+1 + coef * ln(floor((p + 1) / every) + 1) at position p (``q_temp``), and no key / value
+projections at all (``own_kv`` False: the layer attends with its own queries to the keys
+and values of the cache entry the run order names).
 """
 from __future__ import annotations
 
@@ -44,41 +51,68 @@ class AttentionMixer:
         self.qkv: Optional[Linear] = None
         self.out: Optional[Linear] = None
         self.q_norm_weight = self.k_norm_weight = None
+        self.sinks: Optional[torch.Tensor] = None
+        self.own_kv = bool(getattr(spec, "own_kv", True))
+        self.value_dim = int(getattr(spec, "value_dim", 0) or spec.head_dim)
+        qt = getattr(spec, "q_temp", None)
+        self.q_temp = (float(qt.coef), int(qt.every)) if qt is not None and qt.coef != 0 else None
+        if self.q_temp is not None and self.q_temp[1] < 1:
+            raise ValueError("the query temperature's period must be at least 1")
+        # the options the standard kernels' callers do not pass
+        self.plain = (self.own_kv and self.value_dim == spec.head_dim and self.q_temp is None
+                      and not getattr(spec, "sink", False))
 
     @classmethod
     def param_specs(cls, spec: AttentionSpec, hidden_size: int) -> Dict[str, ParamSpec]:
         q, kv = spec.n_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim
-        p = {
-            "q_proj.weight": ParamSpec((q, hidden_size)),
-            "k_proj.weight": ParamSpec((kv, hidden_size)),
-            "v_proj.weight": ParamSpec((kv, hidden_size)),
-            "o_proj.weight": ParamSpec((hidden_size, q)),
-        }
+        vd = getattr(spec, "value_dim", 0) or spec.head_dim
+        own_kv = getattr(spec, "own_kv", True)
+        p = {"q_proj.weight": ParamSpec((q, hidden_size))}
+        if own_kv:
+            p["k_proj.weight"] = ParamSpec((kv, hidden_size))
+            p["v_proj.weight"] = ParamSpec((spec.n_kv_heads * vd, hidden_size))
+        p["o_proj.weight"] = ParamSpec((hidden_size, spec.n_heads * vd))
         if spec.qk_norm is not None:
             zc = spec.qk_norm.zero_centered
             p["q_norm.weight"] = ParamSpec((spec.head_dim,), "norm", zero_centered=zc)
-            p["k_norm.weight"] = ParamSpec((spec.head_dim,), "norm", zero_centered=zc)
+            if own_kv:
+                p["k_norm.weight"] = ParamSpec((spec.head_dim,), "norm", zero_centered=zc)
+        if getattr(spec, "sink", False):
+            p["sink"] = ParamSpec((spec.n_heads,), "float32")
         return p
 
     def cache_request(self):
-        return KVRequest(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window)
+        if not self.own_kv:
+            return None
+        return KVRequest(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window,
+                         0 if self.value_dim == self.spec.head_dim else self.value_dim)
 
     def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype,
              device: torch.device) -> None:
         def mat(name):
             return tensors[name].to(device=device, dtype=dtype)
-        # one product for q | k | v: rows of q first, then k, then v
-        self.qkv = Linear(torch.cat([mat("q_proj.weight"), mat("k_proj.weight"),
-                                     mat("v_proj.weight")], dim=0).contiguous(), role="qkv")
+        # one product for q | k | v: rows of q first, then k, then v (q alone for a layer
+        # without keys and values of its own)
+        if self.own_kv:
+            self.qkv = Linear(torch.cat([mat("q_proj.weight"), mat("k_proj.weight"),
+                                         mat("v_proj.weight")], dim=0).contiguous(), role="qkv")
+        else:
+            self.qkv = Linear(mat("q_proj.weight").contiguous(), role="qkv")
         self.out = Linear(mat("o_proj.weight").contiguous(), role="out_proj")
         if self.spec.qk_norm is not None:
             add = 1.0 if self.spec.qk_norm.zero_centered else 0.0
             self.q_norm_weight = (tensors["q_norm.weight"].to(device=device, dtype=torch.float32)
                                   + add).contiguous()
-            self.k_norm_weight = (tensors["k_norm.weight"].to(device=device, dtype=torch.float32)
-                                  + add).contiguous()
+            if self.own_kv:
+                self.k_norm_weight = (tensors["k_norm.weight"].to(device=device,
+                                                                  dtype=torch.float32)
+                                      + add).contiguous()
+        if getattr(self.spec, "sink", False):
+            self.sinks = tensors["sink"].to(device=device, dtype=torch.float32).contiguous()
 
     def forward(self, x: torch.Tensor, ctx, cache_entry: int, writes_cache: bool) -> torch.Tensor:
+        if not self.plain:
+            return self._forward_options(x, ctx, cache_entry, writes_cache)
         s = self.spec
         nh, nkv, hd = s.n_heads, s.n_kv_heads, s.head_dim
         T = x.shape[0]
@@ -136,6 +170,70 @@ class AttentionMixer:
                                        writes_cache, window)
         out = ctx.new(T, nh * hd)
         kernels.attention_decode(qkv[:, :nh * hd], out, view, ctx, nh, nkv, hd, s.scale, window)
+        return self.out.partial(out)
+
+    def _forward_options(self, x: torch.Tensor, ctx, cache_entry: int,
+                         writes_cache: bool) -> torch.Tensor:
+        """The same flow for a spec with a sink, a query temperature, value heads of their
+        own size or no keys and values of its own: the projection's 32-bit sums are normed,
+        rotated, tempered and rounded once; keys and values go to the cache; prompts attend
+        from the step's tensors and decoding from the cache."""
+        s = self.spec
+        nh, nkv, hd, hdv = s.n_heads, s.n_kv_heads, s.head_dim, self.value_dim
+        if writes_cache != self.own_kv:
+            raise ValueError("a layer without key / value projections must read another call's "
+                             "cache entry, and one with them must write its own")
+        T = x.shape[0]
+        cos = sin = None
+        rotary_dim = 0
+        if self.position is not None:
+            cos, sin = self.position.tables(ctx)
+            rotary_dim = self.position.rotary_dim
+        view = ctx.cache.kv_view(cache_entry)
+        eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
+        window = s.window or 0
+        n_own = nkv if self.own_kv else 0
+        width = (nh + n_own) * hd + n_own * hdv
+        proj = self.qkv.partial(x, cheap_sum=True)
+        part = proj if proj.dim() == 3 else None
+        if (ctx.mode == DECODE and part is not None and hdv == hd and
+                kernels.attention_decode_fused_supported(self.dtype, hd, rotary_dim)):
+            out = ctx.new(T, nh * hdv)
+            kernels.attention_decode_fused(part, self.q_norm_weight, self.k_norm_weight, eps, cos,
+                                           sin, self.own_kv, out, view, ctx, nh, nkv, hd, s.scale,
+                                           window, sinks=self.sinks, q_temp=self.q_temp,
+                                           q_only=not self.own_kv)
+            return self.out.partial(out)
+        qkv = proj if part is None else ctx.new(T, width)
+        vt = None
+        if self.own_kv:
+            if ctx.mode == PREFILL and kernels.attention_prefill_wants_transposed_values(
+                    qkv, hd, hdv):
+                vt = kernels.prefill_values_scratch(T, ctx.batch, nkv, hd, qkv.device)
+            kernels.qk_norm_rope_store(
+                qkv, nh, nkv, hd, self.q_norm_weight, self.k_norm_weight, eps, cos, sin,
+                rotary_dim, ctx.positions, view.k_pool, view.v_pool, view.page_table, ctx.slots,
+                ctx.lens, ctx.seq_index, view.page, view.cap, partial=part, vt=vt,
+                cu_seqlens=ctx.cu_seqlens, max_len=ctx.max_new, value_dim=hdv,
+                q_temp=self.q_temp)
+        else:
+            kernels.qk_norm_rope_store(qkv, nh, 0, hd, self.q_norm_weight, None, eps, cos, sin,
+                                       rotary_dim, ctx.positions, partial=part, value_dim=hdv,
+                                       q_temp=self.q_temp)
+        q = qkv[:, :nh * hd]
+        out = ctx.new(T, nh * hdv)
+        if ctx.mode == PREFILL:
+            if self.own_kv:
+                k = qkv[:, nh * hd:(nh + nkv) * hd]
+                v = qkv[:, (nh + nkv) * hd:]
+                ctx.step_kv[cache_entry] = (k, v, vt)
+            else:
+                k, v, vt = ctx.step_kv[cache_entry]
+            kernels.attention_prefill(q, k, v, out, ctx, nh, nkv, hd, s.scale, window, vt=vt,
+                                      value_dim=hdv, sinks=self.sinks)
+        else:
+            kernels.attention_decode(q, out, view, ctx, nh, nkv, hd, s.scale, window,
+                                     value_dim=hdv, sinks=self.sinks)
         return self.out.partial(out)
 
     def _attend_prompt(self, qkv: torch.Tensor, vt, ctx, cache_entry: int, writes_cache: bool,

@@ -33,6 +33,7 @@ class ParamSpec:
     role "embedding": a table [rows, width], kept in the compute dtype;
     role "norm": a norm weight, kept in 32-bit (``zero_centered`` ones are
     stored as w and used as 1 + w);
+    role "norm_bias": a norm's bias, kept in 32-bit;
     role "table_int": an integer table, kept as int32;
     role "float32": kept in 32-bit whatever the compute dtype is.
     """
@@ -45,10 +46,12 @@ class ParamSpec:
 @dataclass(frozen=True)
 class KVRequest:
     """Keys and values per position; ``window`` None keeps all of them, W keeps
-    the last W."""
+    the last W.  ``value_dim``: the size of a value head where it differs from the
+    keys' ``head_dim`` (0: the same)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: int = 0
 
 
 @dataclass(frozen=True)

@@ -4,6 +4,8 @@
     h += post_mixer_norm(mixer(pre_mixer_norm(h)))
     h += post_ffn_norm(ffn(pre_ffn_norm(h)))
 "pre": the same without the two post norms.
+``residual_mult`` m: every branch joins as h += m * (...).  A spec without a feed-forward
+gives a layer of the mixer branch alone (and no norms of the second branch).
 
 The residual sum, the norm of the branch and the norm that feeds the next
 branch are one kernel launch, so a block receives its input already normed
@@ -29,29 +31,34 @@ class Block:
         self.spec, self.hidden_size, self.dtype, self.device = spec, hidden_size, dtype, device
         N = norm_class(spec.norm.kind)
         self.sandwich = spec.arrangement == "sandwich"
+        self.mult = float(getattr(spec, "residual_mult", 1.0))
+        has_ffn = spec.feed_forward is not None
         self.pre_mixer_norm = N(spec.norm, hidden_size, dtype, device)
-        self.pre_ffn_norm = N(spec.norm, hidden_size, dtype, device)
+        self.pre_ffn_norm = N(spec.norm, hidden_size, dtype, device) if has_ffn else None
         self.post_mixer_norm = N(spec.norm, hidden_size, dtype, device) if self.sandwich else None
-        self.post_ffn_norm = N(spec.norm, hidden_size, dtype, device) if self.sandwich else None
+        self.post_ffn_norm = (N(spec.norm, hidden_size, dtype, device)
+                              if self.sandwich and has_ffn else None)
         self.mixer = mixer_class(spec.mixer.kind)(spec.mixer, hidden_size, dtype, device)
-        self.ffn = feed_forward_class(spec.feed_forward.kind)(spec.feed_forward, hidden_size,
-                                                              dtype, device)
+        self.ffn = (feed_forward_class(spec.feed_forward.kind)(spec.feed_forward, hidden_size,
+                                                               dtype, device) if has_ffn else None)
 
     @classmethod
     def param_specs(cls, spec: BlockSpec, hidden_size: int) -> Dict[str, ParamSpec]:
         N = norm_class(spec.norm.kind)
-        names = ["pre_mixer_norm", "pre_ffn_norm"]
+        has_ffn = spec.feed_forward is not None
+        names = ["pre_mixer_norm"] + (["pre_ffn_norm"] if has_ffn else [])
         if spec.arrangement == "sandwich":
-            names += ["post_mixer_norm", "post_ffn_norm"]
+            names += ["post_mixer_norm"] + (["post_ffn_norm"] if has_ffn else [])
         out: Dict[str, ParamSpec] = {}
         for n in names:
             for k, v in N.param_specs(spec.norm, hidden_size).items():
                 out[f"{n}.{k}"] = v
         for k, v in mixer_class(spec.mixer.kind).param_specs(spec.mixer, hidden_size).items():
             out[f"mixer.{k}"] = v
-        F = feed_forward_class(spec.feed_forward.kind)
-        for k, v in F.param_specs(spec.feed_forward, hidden_size).items():
-            out[f"ffn.{k}"] = v
+        if has_ffn:
+            F = feed_forward_class(spec.feed_forward.kind)
+            for k, v in F.param_specs(spec.feed_forward, hidden_size).items():
+                out[f"ffn.{k}"] = v
         return out
 
     @property
@@ -72,28 +79,42 @@ class Block:
             if part is not None:
                 part.load(sub(name), device)
         self.mixer.load(sub("mixer"), dtype, device)
-        self.ffn.load(sub("ffn"), dtype, device)
+        if self.ffn is not None:
+            self.ffn.load(sub("ffn"), dtype, device)
 
     def forward(self, h: torch.Tensor, x: torch.Tensor, ctx, cache_entry: int,
                 writes_cache: bool, next_norm) -> Optional[torch.Tensor]:
         """h: [T, H] 32-bit stream (updated in place); x = pre_mixer_norm(h)."""
         y = self.mixer.forward(x, ctx, cache_entry, writes_cache)
+        if self.ffn is None:
+            x3 = ctx.new(*x.shape) if next_norm is not None else None
+            _join(h, y, self.post_mixer_norm, next_norm, x3, self.mult)
+            return x3
         x2 = ctx.new(*x.shape)
-        _join(h, y, self.post_mixer_norm, self.pre_ffn_norm, x2)
+        _join(h, y, self.post_mixer_norm, self.pre_ffn_norm, x2, self.mult)
         d = self.ffn.forward(x2, ctx)
         x3 = ctx.new(*x.shape) if next_norm is not None else None
-        _join(h, d, self.post_ffn_norm, next_norm, x3)
+        _join(h, d, self.post_ffn_norm, next_norm, x3, self.mult)
         return x3
 
 
 register_block("sequential", Block)
 
 
-def _join(h, y, post, nxt, x_out) -> None:
-    """h += post(y) (or y when there is no post norm); x_out = nxt(h) if nxt."""
-    if post is not None:
-        post.residual(h, y, nxt, x_out)
+def _join(h, y, post, nxt, x_out, mult: float = 1.0) -> None:
+    """h += mult * post(y) (or mult * y when there is no post norm); x_out = nxt(h) if nxt."""
+    if mult == 1.0:
+        # (parts registered from outside may know nothing of a multiplier)
+        if post is not None:
+            post.residual(h, y, nxt, x_out)
+        elif nxt is not None:
+            nxt.after_residual(h, y, x_out)
+        else:
+            fused_residual(h, y, None, None, None)
+    elif post is not None:
+        post.residual(h, y, nxt, x_out, mult)
     elif nxt is not None:
-        nxt.after_residual(h, y, x_out)
+        nxt.after_residual(h, y, x_out, mult)
     else:
-        fused_residual(h, y, None, None, None)
+        from .. import kernels
+        kernels.layer_norm_join(h, y, None, None, None, None, None, mult=mult)

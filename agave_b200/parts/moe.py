@@ -1,0 +1,91 @@
+"""Routed feed-forward (mixture of experts) as a feed-forward part.
+
+Every token uses ``top`` of ``n_experts`` small gated feed-forwards
+down_e(act(gate_e x) * up_e x).  Router: s = sigmoid(W_r x) in 32-bit; the choice scores
+s + correction pick (restricted to the experts of the best ``keep_groups`` of ``n_groups``
+equal groups of neighbours, a group scoring the sum of its two largest choice scores), the
+plain s weigh, not renormalised; the output is the weighted sum of the chosen experts'.
+
+Flow of a step (all decided on the device, so a step records into a CUDA graph):
+router -> plan (the (token, choice) pairs laid out by expert, each expert's run padded to
+the row tile) -> gate/up as one grouped product with the activation in its epilogue ->
+down as a grouped product whose epilogue multiplies by the pair's weight and scatters to
+[choice, token, :].  That 32-bit tensor is returned as partial sums: the norm that
+follows adds the choices in order, as it adds the ranges of K of a dense projection.
+
+The experts' matrices are stacked [E, ...] at load time so that a tile finds its expert
+by index.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import kernels
+from ..config.base import RoutedFeedForwardSpec
+from .base import ParamSpec, register_feed_forward
+
+
+class RoutedFeedForward:
+    def __init__(self, spec: RoutedFeedForwardSpec, hidden_size: int, dtype: torch.dtype,
+                 device: torch.device):
+        if spec.n_experts % spec.n_groups:
+            raise ValueError("the experts must form equal groups")
+        if not 1 <= spec.keep_groups <= spec.n_groups:
+            raise ValueError("keep_groups must lie in 1..n_groups")
+        if spec.top > spec.keep_groups * (spec.n_experts // spec.n_groups):
+            raise ValueError("top exceeds the experts of the groups kept")
+        self.spec, self.hidden_size, self.dtype = spec, hidden_size, dtype
+        self.w_router: Optional[torch.Tensor] = None
+        self.correction: Optional[torch.Tensor] = None
+        self.w_gate = self.w_up = self.w_down = None
+
+    @classmethod
+    def param_specs(cls, spec: RoutedFeedForwardSpec, hidden_size: int) -> Dict[str, ParamSpec]:
+        ff = spec.intermediate_size
+        p = {"router.weight": ParamSpec((spec.n_experts, hidden_size))}
+        if spec.correction:
+            p["router.correction"] = ParamSpec((spec.n_experts,), "float32")
+        for e in range(spec.n_experts):
+            p[f"experts.{e}.gate_proj.weight"] = ParamSpec((ff, hidden_size))
+            p[f"experts.{e}.up_proj.weight"] = ParamSpec((ff, hidden_size))
+            p[f"experts.{e}.down_proj.weight"] = ParamSpec((hidden_size, ff))
+        return p
+
+    def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype,
+             device: torch.device) -> None:
+        def stack(name):
+            return torch.stack([tensors[f"experts.{e}.{name}.weight"].to(device=device, dtype=dtype)
+                                for e in range(self.spec.n_experts)]).contiguous()
+        self.w_router = tensors["router.weight"].to(device=device, dtype=dtype).contiguous()
+        if self.spec.correction:
+            self.correction = tensors["router.correction"].to(
+                device=device, dtype=torch.float32).contiguous()
+        self.w_gate, self.w_up, self.w_down = stack("gate_proj"), stack("up_proj"), stack("down_proj")
+
+    def route(self, x: torch.Tensor):
+        """(ids [T, top] int32, weights [T, top] 32-bit) of the tokens of x."""
+        s = self.spec
+        T = x.shape[0]
+        ids = torch.empty((T, s.top), dtype=torch.int32, device=x.device)
+        wts = torch.empty((T, s.top), dtype=torch.float32, device=x.device)
+        kernels.moe_route(x, self.w_router, self.correction, s.n_groups, s.keep_groups, s.top,
+                          ids, wts)
+        return ids, wts
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        s = self.spec
+        T, H = x.shape
+        ids, wts = self.route(x)
+        plan = kernels.moe_plan(ids, wts, s.n_experts)
+        z = torch.empty((plan.rows, s.intermediate_size), dtype=x.dtype, device=x.device)
+        kernels.moe_grouped(x, self.w_gate, z, plan, w2=self.w_up, activation=s.activation,
+                            gather=True, op="experts_gate_up")
+        y = torch.empty((s.top, T, H), dtype=torch.float32, device=x.device)
+        kernels.moe_grouped(z, self.w_down, y.view(s.top * T, H), plan, scatter=True,
+                            op="experts_down")
+        return y
+
+
+register_feed_forward("routed", RoutedFeedForward)

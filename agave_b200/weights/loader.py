@@ -84,7 +84,10 @@ def head_is_stored(folder: str, checkpoint_name: Callable[[str, str], str],
     files = SafetensorsFolder(folder)
     prefix = choose_prefix(files.names(), [checkpoint_name("embed.weight", ""),
                                            checkpoint_name("final_norm.weight", "")], prefixes)
-    return checkpoint_name("lm_head.weight", prefix) in files.tensors
+    try:
+        return checkpoint_name("lm_head.weight", prefix) in files.tensors
+    except KeyError:
+        return False            # the architecture has no head of its own at all
 
 
 class LoadedWeights(dict):

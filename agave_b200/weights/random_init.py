@@ -37,6 +37,10 @@ def random_tensor(name: str, spec: ParamSpec, seed: int, std: float, norm_std: f
         if not spec.zero_centered:
             t = t + 1.0
         return t.to(dtype)
+    if spec.role in ("norm_bias", "float32"):
+        # biases of norms and small learned vectors (sink logits, router corrections):
+        # around zero, on the norms' scale
+        return (t * norm_std).to(dtype)
     return (t * std).to(dtype)
 
 
