@@ -315,6 +315,62 @@ def moe_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: MoePl
             ACT[activation], _stream()))
 
 
+def moe_grouped_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether ``moe_grouped_tc`` takes these operands: bfloat16, K and the row stride
+    multiples of 8, 16-byte aligned."""
+    return (_MOE_TC and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and
+            w.shape[2] % 8 == 0 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and
+            w.data_ptr() % 16 == 0)
+
+
+_MOE_TC = os.environ.get("AGAVE_B200_MOE_TENSOR_CORES", "1") != "0"
+
+
+def moe_gather_rows(x: torch.Tensor, plan: MoePlan, xs: torch.Tensor) -> None:
+    """xs [plan.rows, H] = the rows of x [T, H] in the plan's sorted order (zeros where the
+    plan pads), bfloat16."""
+    T, H = x.shape
+    assert x.dtype == torch.bfloat16 and xs.dtype == torch.bfloat16 and x.stride(1) == 1
+    _dense(xs, "xs")
+    assert xs.shape == (plan.rows, H)
+    with _span("experts_gather", _nbytes(xs) * 2):
+        _check(library().agv_moe_gather_rows(_ptr(x), ctypes.c_longlong(x.stride(0)),
+                                             _ptr(plan.tok), _ptr(xs), plan.rows, H, _stream()))
+
+
+def moe_grouped_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: MoePlan,
+                   w2: Optional[torch.Tensor] = None, activation: str = "silu",
+                   scatter: bool = False, op: str = "experts") -> None:
+    """``moe_grouped`` in bfloat16 on the tensor cores; a's rows are sorted positions
+    ([plan.rows, K]).  Gated: out [plan.rows, N] bfloat16.  Plain: out 32-bit, with
+    ``scatter`` [top * T, N] rows at [choice * T + token] times the pair's weight."""
+    E, N, K = w.shape
+    _dense(w, "w")
+    assert a.shape == (plan.rows, K) and a.stride(1) == 1 and out.stride(1) == 1
+    assert out.shape[1] == N and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    if w2 is not None:
+        _dense(w2, "w2")
+        assert w2.shape == w.shape and w2.dtype == w.dtype and out.dtype == torch.bfloat16
+        assert not scatter and out.shape[0] == plan.rows
+    else:
+        assert out.dtype == torch.float32
+    pairs = plan.T * plan.top
+    n = 2 if w2 is not None else 1
+    with _span(op, n * min(E, pairs) * N * K * 2 + pairs * (K + N) * 2, 2 * n * pairs * N * K):
+        _check(library().agv_moe_grouped_tc(
+            _ptr(a), ctypes.c_longlong(a.stride(0)), plan.rows, _ptr(plan.tok), _ptr(w), _ptr(w2),
+            E, _ptr(out), ctypes.c_longlong(out.stride(0)), _ptr(plan.dst) if scatter else None,
+            _ptr(plan.wpos) if scatter else None, _ptr(plan.tile_e), plan.tiles, N, K,
+            ACT[activation], _stream()))
+
+
+def moe_tc_status() -> int:
+    """0, or the code of the first bounded wait of the grouped tensor-core kernel that gave
+    up since the last call (this call synchronises the device)."""
+    torch.cuda.synchronize()
+    return library().agv_moe_tc_status()
+
+
 # ------------------------------------------------------------ matrix products
 def _linear_cost(x, w, w2, out):
     """(bytes, flops) of a projection: weights and operands once, 2 T N K flops."""

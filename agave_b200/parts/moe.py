@@ -10,7 +10,9 @@ Flow of a step (all decided on the device, so a step records into a CUDA graph):
 router -> plan (the (token, choice) pairs laid out by expert, each expert's run padded to
 the row tile) -> gate/up as one grouped product with the activation in its epilogue ->
 down as a grouped product whose epilogue multiplies by the pair's weight and scatters to
-[choice, token, :].  That 32-bit tensor is returned as partial sums: the norm that
+[choice, token, :].  In bfloat16 the grouped products run on the tensor cores (tcgen05 +
+TMA, ``csrc/moe_tcgen05.cu``), in 32-bit and for odd sizes as FFMA dot products
+(``csrc/moe.cu``).  That 32-bit tensor is returned as partial sums: the norm that
 follows adds the choices in order, as it adds the ranges of K of a dense projection.
 
 The experts' matrices are stacked [E, ...] at load time so that a tile finds its expert
@@ -80,9 +82,20 @@ class RoutedFeedForward:
         ids, wts = self.route(x)
         plan = kernels.moe_plan(ids, wts, s.n_experts)
         z = torch.empty((plan.rows, s.intermediate_size), dtype=x.dtype, device=x.device)
+        y = torch.empty((s.top, T, H), dtype=torch.float32, device=x.device)
+        if (kernels.moe_grouped_tc_supported(x, self.w_gate) and
+                kernels.moe_grouped_tc_supported(z, self.w_down)):
+            # bfloat16 on the tensor cores: the tokens are brought into the plan's order
+            # first, so that a tile's rows come as one TMA box
+            xs = torch.empty((plan.rows, H), dtype=x.dtype, device=x.device)
+            kernels.moe_gather_rows(x, plan, xs)
+            kernels.moe_grouped_tc(xs, self.w_gate, z, plan, w2=self.w_up,
+                                   activation=s.activation, op="experts_gate_up")
+            kernels.moe_grouped_tc(z, self.w_down, y.view(s.top * T, H), plan, scatter=True,
+                                   op="experts_down")
+            return y
         kernels.moe_grouped(x, self.w_gate, z, plan, w2=self.w_up, activation=s.activation,
                             gather=True, op="experts_gate_up")
-        y = torch.empty((s.top, T, H), dtype=torch.float32, device=x.device)
         kernels.moe_grouped(z, self.w_down, y.view(s.top * T, H), plan, scatter=True,
                             op="experts_down")
         return y

@@ -24,6 +24,14 @@ every timed iteration reads them from HBM; ``config.l2`` says how many bytes.
 ``--layers``, ``--prompt-lens`` and ``--prefill-tokens`` measure fewer layers,
 other contexts and other prompts; what they were is in ``config`` and
 ``prefill``.
+
+``--compare ramilorn`` is another measurement altogether (the default workload and its
+JSON line are untouched by it): the Ramilorn decoder at a few layer sizes beside a
+Gemma 3 decoder of equal size (same width, heads, head size, layers and vocabulary, a
+dense feed-forward as wide as the experts a token uses), random weights, one JSON line
+with, per size and model, prefill and decode throughput (recorded steps, CUDA events)
+and every operation's device time with its share of the measured peaks
+(``agave_b200.perf``, steps run launch by launch).
 """
 import argparse
 import json
@@ -214,6 +222,124 @@ def timed_decode(engine, torch, batch, steps, warmup, seed, lo=128, hi=2048):
     return ms, final_lens, per_step
 
 
+# Ramilorn layer sizes for --compare: (width, heads, kv heads, head size, experts, experts per
+# token, expert width, groups, groups kept, layers, vocabulary).  Every second layer
+# attends to the keys and values of the layer before it.
+COMPARE_SIZES = {
+    "small": (1024, 16, 4, 64, 16, 2, 512, 4, 2, 8, 32768),
+    "medium": (2048, 16, 4, 128, 32, 4, 768, 8, 4, 8, 65536),
+    "large": (4096, 32, 8, 128, 64, 6, 1408, 8, 4, 4, 65536),
+}
+
+
+def compare_configs(size):
+    H, A, G, d, E, top, ff, groups, keep, L, V = COMPARE_SIZES[size]
+    mixer = {"dim": d, "heads": A, "kv_heads": G, "q_temp": {"coef": 0.1, "every": 1024},
+             "scale": d ** -0.5, "vdim": d}
+    mlp = {"expert": {"ff": ff}, "kind": "moe",
+           "router": {"experts": E, "groups": {"count": groups, "keep": keep}, "top": top}}
+    layers = []
+    for l in range(L):
+        m = dict(mixer)
+        if l % 2 == 1:
+            m["kv_from"] = l - 1
+        layers.append({"mixer": m, "mlp": mlp, "type": "attention"})
+    ramilorn = {"architecture": "Ramilorn", "layers": layers, "logit_softcap": 30.0,
+                "norm": {"eps": 1e-5}, "residual_mult": 0.5, "vocab": V, "width": H}
+    gemma = dict(CONFIG_1B, num_hidden_layers=L, hidden_size=H, num_attention_heads=A,
+                 num_key_value_heads=G, head_dim=d, query_pre_attn_scalar=d,
+                 intermediate_size=top * ff, vocab_size=V, sliding_window=None,
+                 sliding_window_pattern=0, hidden_activation="silu")
+    return ramilorn, gemma
+
+
+def run_compare(args):
+    import torch
+    from agave_b200 import kernels
+    from agave_b200.config import resolve_architecture
+    from agave_b200.engine.api import Engine
+    from agave_b200.models.decoder import decoder_param_specs
+    from agave_b200.perf import PerfCounters
+    from agave_b200.weights import random_tensors
+    pk = peaks()
+    batch, ctx_len, n_pre = 8, 1024, args.prefill_tokens
+    out = {"compare": "ramilorn beside gemma3 at equal size", "dtype": "bf16", "data": "synthetic",
+           "decode_batch": batch, "decode_context": ctx_len, "prefill_tokens": n_pre,
+           "peaks": pk, "sizes": {}}
+    for size in (args.compare_sizes or sorted(COMPARE_SIZES)):
+        entry = {}
+        for name, cfg in zip(("ramilorn", "gemma3"), compare_configs(size)):
+            arch = resolve_architecture(cfg)
+            specs = decoder_param_specs(arch.config_class.from_dict(cfg).to_model_spec())
+            tensors = random_tensors(specs, 11, 0.02, 0.1, torch.bfloat16, "cuda:0")
+            for k, t in tensors.items():
+                if k.endswith("router.weight"):
+                    t.mul_(60.0)      # router logits of order one: tokens spread over the experts
+            engine = Engine(None, _raw_config=cfg, _tensors=tensors, dtype="bfloat16",
+                            max_tokens=batch * 4096, ctx_size=4096, max_batch=batch)
+            del tensors
+            V = engine.spec.vocab_size
+            g = torch.Generator().manual_seed(3)
+            prompt = torch.randint(3, V, (n_pre,), generator=g).tolist()
+
+            def timed_prompt(tokens):
+                s = engine.acquire()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                e0.record()
+                engine.step([(s, tokens)], [[len(tokens) - 1]])
+                e1.record()
+                torch.cuda.synchronize()
+                engine.release(s)
+                return e0.elapsed_time(e1)
+            pre = sorted(timed_prompt(prompt) for _ in range(3 + 5))[:5]
+            pre_ms = pre[len(pre) // 2]
+            ms, _, launches = timed_decode(engine, torch, batch, args.steps, max(3, args.warmup), 8,
+                                           ctx_len, ctx_len)
+            # every operation's device time, launch by launch
+            ops = {}
+            for what in ("prefill", "decode"):
+                counters = PerfCounters()
+                if what == "prefill":
+                    for rep in range(3):
+                        slot = engine.acquire()
+                        if rep == 2:
+                            counters.__enter__()
+                        engine.step([(slot, prompt)], [[n_pre - 1]])
+                        engine.release(slot)
+                else:
+                    slots = [engine.acquire() for _ in range(batch)]
+                    engine.step([(s, prompt[:ctx_len]) for s in slots], [[] for _ in slots])
+                    for rep in range(3):
+                        if rep == 2:
+                            counters.__enter__()
+                        engine.step([(s, [5 + rep]) for s in slots], [[0] for _ in slots])
+                    for s in slots:
+                        engine.release(s)
+                table = counters.table()
+                counters.__exit__()
+                rows = {}
+                for op, r in table.items():
+                    sec = r["total_us"] * 1e-6
+                    gbs = r["bytes"] / sec / 1e9 if sec > 0 else 0.0
+                    tf = r["flops"] / sec / 1e12 if sec > 0 else 0.0
+                    rows[op] = {"calls": r["calls"], "us": round(r["total_us"] / r["calls"], 2),
+                                "gbs": round(gbs, 1), "tflops": round(tf, 2),
+                                "of_peak": round(max(gbs / pk["hbm_gbs"], tf / pk["bf16_tflops"]), 4)}
+                ops[what] = rows
+            entry[name] = {"prefill_ms": round(pre_ms, 3),
+                           "prefill_tokens_per_s": round(n_pre / pre_ms * 1e3, 1),
+                           "decode_ms_per_step": round(ms, 4),
+                           "decode_tokens_per_s": round(batch / ms * 1e3, 1),
+                           "kernels_per_decode_step": launches,
+                           "weight_gb": round(engine.model.weight_bytes() / 1e9, 3), "ops": ops}
+            del engine
+            torch.cuda.empty_cache()
+        out["sizes"][size] = entry
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -229,7 +355,17 @@ def main():
                          "schedule's, 128 to 2,048 for the benchmark configuration)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="length of the timed prompt (default: the benchmark configuration's)")
+    ap.add_argument("--compare", default=None, choices=["ramilorn"],
+                    help="instead of the benchmark: this architecture beside Gemma 3 at equal "
+                         "layer sizes (see the module text)")
+    ap.add_argument("--compare-sizes", nargs="+", default=None, choices=sorted(COMPARE_SIZES),
+                    help="the sizes --compare runs (default: all)")
     args = ap.parse_args()
+    if args.compare and args.impl == "ours":
+        if args.gpus != 1:
+            print("bench.py: this library runs on one GPU; --gpus must be 1")
+            return 2
+        return run_compare(args)
     sched = SCHEDULES[args.shapes]
     lo, hi = args.prompt_lens or sched["lens"]
     steps = args.steps if sched["steps"] is None else sched["steps"]

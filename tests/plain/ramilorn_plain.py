@@ -124,8 +124,16 @@ def expert(x: torch.Tensor, w: Dict[str, torch.Tensor], pre: str) -> torch.Tenso
     return (g * torch.sigmoid(g) * u) @ w[pre + "down"].T
 
 
-def moe(x: torch.Tensor, w: Dict[str, torch.Tensor], pre: str, mlp: dict) -> torch.Tensor:
-    ids, wt = route(x, w[pre + "router"], w[pre + "correction"], mlp["router"])
+def moe(x: torch.Tensor, w: Dict[str, torch.Tensor], pre: str, mlp: dict,
+        ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``ids`` [T, top] given: those experts are used instead of the router's own choice
+    (their weights are still this router's scores): for comparisons in reduced precision,
+    where a close call may fall the other way."""
+    own, wt = route(x, w[pre + "router"], w[pre + "correction"], mlp["router"])
+    if ids is None:
+        ids = own
+    else:
+        wt = torch.gather(torch.sigmoid(x @ w[pre + "router"].T), 1, ids.long())
     y = torch.zeros_like(x)
     for t in range(x.shape[0]):
         for e, a in zip(ids[t].tolist(), wt[t]):
@@ -139,8 +147,10 @@ def soft_cap(z: torch.Tensor, cap: float) -> torch.Tensor:
 
 # ---------------------------------------------------------------------- model
 def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int],
-            streams: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
-    """Logits [T, V] of one sequence; ``streams`` collects the stream after each layer."""
+            streams: Optional[List[torch.Tensor]] = None,
+            experts: Optional[Dict[int, torch.Tensor]] = None) -> torch.Tensor:
+    """Logits [T, V] of one sequence; ``streams`` collects the stream after each layer;
+    ``experts`` {layer: ids [T, top]} fixes the experts of those layers (see ``moe``)."""
     eps = float(cfg["norm"]["eps"])
     mult = float(cfg["residual_mult"])
 
@@ -159,7 +169,8 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int],
                                      kept[src] if src is not None else None)
         x = x + mult * norm(y, p + "norm1b")
         if layer.get("mlp") is not None:
-            y = moe(norm(x, p + "norm2"), w, p + "mlp.", layer["mlp"])
+            y = moe(norm(x, p + "norm2"), w, p + "mlp.", layer["mlp"],
+                    None if experts is None else experts.get(i))
             x = x + mult * norm(y, p + "norm2b")
         if streams is not None:
             streams.append(x.clone())

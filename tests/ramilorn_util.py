@@ -142,6 +142,6 @@ def tokens(n, vocab, seed):
     return torch.randint(0, vocab, (n,), generator=g).tolist()
 
 
-def plain_logits(folder, toks, streams=None):
+def plain_logits(folder, toks, streams=None, experts=None):
     from plain import ramilorn_plain as P
-    return P.forward(P.read_config(folder), P.read_weights(folder), toks, streams)
+    return P.forward(P.read_config(folder), P.read_weights(folder), toks, streams, experts)

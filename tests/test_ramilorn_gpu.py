@@ -4,12 +4,14 @@ whole prompts, the last tokens one by one, unequal batches against each request 
 slots and pages used again, lengths round page borders, long decoding across steps of the
 query temperature, greedy generation, and trace replay as a separate process.
 
-32-bit runs are compared sharply, row by row.  In bfloat16 a router's choice flips where
-two choice scores are closer than the rounding of its input (with random weights and
-several experts per token that is a few rows in a hundred per layer), which moves that
-row's logits by far more than rounding does; so bfloat16 model runs ask that the typical
-row agrees within rounding and that at most a quarter of the rows are off, and the
-mechanisms are compared one by one on inputs without close calls.
+32-bit runs are compared sharply, row by row, with the plain model's own routing.  In
+bfloat16 a router's choice flips where two choice scores are closer than the rounding of its
+input (with random weights and several experts per token that is a few rows in a hundred
+per layer), which moves that row's logits, and in a short sequence every later row's, by
+far more than rounding does.  So in bfloat16 a request that runs alone is compared with the
+plain model *under the experts the library chose* (recorded from its router part; the
+router itself is compared on its own, on inputs without close calls), and batches and
+trace replay are compared with the same request run alone through the library.
 """
 import json
 import math
@@ -40,19 +42,75 @@ def rel_err(got, ref):
 
 
 def rows_agree(got, ref, dtype, what=""):
-    """Logit rows against the plain model: every row in 32-bit; in bfloat16 all but a few
-    (see the module text)."""
+    """Logit rows against reference rows: max error over the row's greatest logit."""
     got, ref = got.detach().double().cpu(), ref.detach().double().cpu()
     assert got.shape == ref.shape, (got.shape, ref.shape)
     assert torch.isfinite(got).all()
     err = (got - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)
+    # (bfloat16: the test models' weights are strong, so that faults show; five layers of
+    # bfloat16 rounding then come to several hundredths of the greatest logit)
+    tol = 3e-4 if dtype == "float32" else 1e-1
+    assert err.max().item() <= tol, \
+        f"{what}: row {err.argmax().item()} of {len(err)} off by {err.max().item():.2e}"
+
+
+class chosen_experts:
+    """Records, while it is open, the experts every routed layer of an engine chooses:
+    ``.ids()`` gives {layer: [tokens seen, top]} in the order the tokens came."""
+
+    def __init__(self, eng):
+        self.eng, self.seen, self.saved = eng, {}, []
+
+    def __enter__(self):
+        # (a recorded prompt step replays without calling the parts: off while recording)
+        self.graphs, self.eng.runner.use_graphs = self.eng.runner.use_graphs, False
+        for call in self.eng.model.spec.schedule:
+            ffn = self.eng.model.blocks[call.block].ffn
+            if ffn is None:
+                continue
+            route = ffn.route
+            self.saved.append((ffn, route))
+
+            def recording(x, _route=route, _layer=call.block):
+                ids, wts = _route(x)
+                self.seen.setdefault(_layer, []).append(ids.cpu())
+                return ids, wts
+            ffn.route = recording
+        return self
+
+    def __exit__(self, *exc):
+        self.eng.runner.use_graphs = self.graphs
+        for ffn, route in self.saved:
+            ffn.route = route
+
+    def ids(self):
+        return {k: torch.cat(v) for k, v in self.seen.items()}
+
+    def ids_of(self, steps, request):
+        """The same for one request of a batch: ``steps`` lists, step by step, the
+        (request, tokens brought) pairs in batch order."""
+        out = {}
+        for layer, calls in self.seen.items():
+            rows = []
+            for call, step in zip(calls, steps):
+                o = 0
+                for r, n in step:
+                    if r == request:
+                        rows.append(call[o:o + n])
+                    o += n
+            out[layer] = torch.cat(rows)
+        return out
+
+
+def reference(eng, folder, toks, dtype, run):
+    """The plain logits of one request: ``run()`` drives the engine over exactly these
+    tokens, in order; in bfloat16 the plain model then uses the experts recorded."""
     if dtype == "float32":
-        assert err.max().item() <= 3e-4, f"{what}: worst row {err.argmax().item()} off by {err.max().item():.2e}"
-    else:
-        bad = (err > 5e-2).sum().item()
-        assert bad <= max(1, int(0.25 * len(err))), f"{what}: {bad} of {len(err)} rows off, worst {err.max().item():.2e}"
-        if len(err) >= 8:
-            assert err.median().item() < 2e-2, f"{what}: median row off by {err.median().item():.2e}"
+        got = run()
+        return got, plain_logits(folder, toks)
+    with chosen_experts(eng) as rec:
+        got = run()
+    return got, plain_logits(folder, toks, experts=rec.ids())
 
 
 # ======================================================================= mechanisms
@@ -164,6 +222,49 @@ def test_routed_feed_forward(dtype, E, G, keep, top, T):
     err = (got - ref).abs().amax(dim=1) / ref.abs().amax()
     tol = 2e-5 if dtype == "float32" else 2e-2
     assert (err > tol).sum().item() <= (0 if dtype == "float32" else max(1, T // 20)), err.max()
+
+
+@pytest.mark.parametrize("T", [3, 130, 700])
+@pytest.mark.parametrize("H, ff, E, top", [(200, 328, 5, 2), (64, 136, 3, 3), (264, 64, 16, 4)])
+def test_experts_on_the_tensor_cores(T, H, ff, E, top):
+    """bfloat16 with sizes that span several weight tiles and leave tails of K and N: the
+    tcgen05 grouped products against the plain experts under the library's own routing, and
+    against the dot-product form bit for bit in what they choose."""
+    from agave_b200 import kernels
+    from agave_b200.config import RoutedFeedForwardSpec
+    from agave_b200.parts import RoutedFeedForward
+    td = torch.bfloat16
+    g = torch.Generator().manual_seed(T + H)
+    spec = RoutedFeedForwardSpec(n_experts=E, top=top, intermediate_size=ff)
+    t = {"router.weight": (torch.randn(E, H, generator=g) * (2.0 / H ** 0.5)).to(td),
+         "router.correction": torch.randn(E, generator=g) * 0.3}
+    for e in range(E):
+        t[f"experts.{e}.gate_proj.weight"] = (torch.randn(ff, H, generator=g) * H ** -0.5).to(td)
+        t[f"experts.{e}.up_proj.weight"] = (torch.randn(ff, H, generator=g) * H ** -0.5).to(td)
+        t[f"experts.{e}.down_proj.weight"] = (torch.randn(H, ff, generator=g) * ff ** -0.5).to(td)
+    part = RoutedFeedForward(spec, H, td, torch.device(DEV))
+    part.load(t, td, torch.device(DEV))
+    x = torch.randn(T, H, generator=g).to(td).to(DEV)
+    assert kernels.moe_grouped_tc_supported(x, part.w_gate)
+    y = part.forward(x, None).sum(0).double().cpu()
+    assert kernels.moe_tc_status() == 0
+    ids, wts = part.route(x)
+    ids, wts = ids.cpu().long(), wts.cpu().double()
+    ref = torch.zeros(T, H, dtype=torch.float64)
+    w = {f"e{e}.{n}": t[f"experts.{e}.{n}_proj.weight"].double() for e in range(E)
+         for n in ("gate", "up", "down")}
+    for e in range(E):
+        rows, slot = (ids == e).nonzero(as_tuple=True)
+        if len(rows):
+            ref[rows] += wts[rows, slot][:, None] * P.expert(x.double().cpu()[rows], w, f"e{e}.")
+    assert rel_err(y, ref) < 1.5e-2
+    # the dot-product form of the same step
+    plan = kernels.moe_plan(*part.route(x), E)
+    z = torch.empty(plan.rows, ff, dtype=td, device=DEV)
+    y2 = torch.empty(top, T, H, dtype=torch.float32, device=DEV)
+    kernels.moe_grouped(x, part.w_gate, z, plan, w2=part.w_up, activation="silu", gather=True)
+    kernels.moe_grouped(z, part.w_down, y2.view(top * T, H), plan, scatter=True)
+    assert rel_err(y2.sum(0), ref) < 1.5e-2
 
 
 def _sink_case(T, A, G, d, dv, seed, spike=None):
@@ -388,10 +489,14 @@ def test_whole_prompts_alone(name, dtype):
     eng, folder = engine_for(name, dtype)
     for n, seed in ((1, 1), (2, 2), (9, 3), (40, 4), (230, 5)):
         toks = tokens(n, vocab(name), seed)
-        s = eng.acquire()
-        got = eng.step([(s, toks)], [list(range(n))])
-        eng.release(s)
-        rows_agree(got, plain_logits(folder, toks), dtype, f"{name} {n} tokens")
+
+        def run():
+            s = eng.acquire()
+            got = eng.step([(s, toks)], [list(range(n))])
+            eng.release(s)
+            return got
+        got, ref = reference(eng, folder, toks, dtype, run)
+        rows_agree(got, ref, dtype, f"{name} {n} tokens")
 
 
 @pytest.mark.parametrize("name", NAMES)
@@ -420,6 +525,16 @@ def test_the_stream_after_every_layer(name):
         assert rel_err(h, streams[upto - 1]) < 2e-5, f"layer {upto - 1}"
 
 
+def alone(eng, toks, cut):
+    """A request by itself: ``cut`` tokens as the prompt, the rest one by one; all rows."""
+    s = eng.acquire()
+    got = [eng.step([(s, toks[:cut])], [list(range(cut))])]
+    for p in range(cut, len(toks)):
+        got.append(eng.step([(s, [toks[p]])], [[0]]))
+    eng.release(s)
+    return torch.cat(got)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
 def test_prompt_then_tokens_one_by_one(name, dtype):
@@ -428,13 +543,8 @@ def test_prompt_then_tokens_one_by_one(name, dtype):
     eng, folder = engine_for(name, dtype)
     for n, cut in ((100, 60), (41, 1), (200, 127)):
         toks = tokens(n, vocab(name), 11 + n)
-        ref = plain_logits(folder, toks)
-        s = eng.acquire()
-        got = [eng.step([(s, toks[:cut])], [list(range(cut))])]
-        for p in range(cut, n):
-            got.append(eng.step([(s, [toks[p]])], [[0]]))
-        eng.release(s)
-        rows_agree(torch.cat(got), ref, dtype, f"{name} {n}/{cut}")
+        got, ref = reference(eng, folder, toks, dtype, lambda: alone(eng, toks, cut))
+        rows_agree(got, ref, dtype, f"{name} {n}/{cut}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -442,12 +552,15 @@ def test_prompt_then_tokens_one_by_one(name, dtype):
 def test_unequal_batches_and_slots_used_again(name, dtype):
     """Three requests of unequal lengths start together and are decoded together, the
     shorter ones ending earlier; then other requests take the freed slots and pages.
-    Every row is compared with the plain model run on that request alone."""
+    Every row is compared with the plain model run on that request alone (in bfloat16 under
+    the experts the batch run chose for that request's tokens)."""
     eng, folder = engine_for(name, dtype)
     V = vocab(name)
     for round_, lens in enumerate([(130, 3, 64), (1, 65, 20), (63, 70, 5)]):
         seqs = [tokens(n + 6 + 3 * i, V, 50 + 10 * round_ + i) for i, n in enumerate(lens)]
-        refs = [plain_logits(folder, s) for s in seqs]
+        rec = chosen_experts(eng)
+        rec.__enter__()
+        steps = [[(i, n) for i, n in enumerate(lens)]]
         slots = [eng.acquire() for _ in seqs]
         got = [[] for _ in seqs]
         out = eng.step([(sl, s[:n]) for sl, s, n in zip(slots, seqs, lens)],
@@ -459,14 +572,18 @@ def test_unequal_batches_and_slots_used_again(name, dtype):
         at = list(lens)
         while any(a < len(s) for a, s in zip(at, seqs)):
             live = [i for i in range(len(seqs)) if at[i] < len(seqs[i])]
+            steps.append([(i, 1) for i in live])
             out = eng.step([(slots[i], [seqs[i][at[i]]]) for i in live], [[0]] * len(live))
             for r, i in enumerate(live):
                 got[i].append(out[r:r + 1])
                 at[i] += 1
                 if at[i] == len(seqs[i]):
                     eng.release(slots[i])
+        rec.__exit__()
         for i in range(len(seqs)):
-            rows_agree(torch.cat(got[i]), refs[i], dtype, f"{name} round {round_} request {i}")
+            ref = plain_logits(folder, seqs[i], experts=None if dtype == "float32"
+                               else rec.ids_of(steps, i))
+            rows_agree(torch.cat(got[i]), ref, dtype, f"{name} round {round_} request {i}")
 
 
 @pytest.mark.parametrize("name", ["R1", "R3"])
@@ -491,12 +608,8 @@ def test_long_decoding(name, dtype):
     """300 tokens decoded after a prompt of 5: several pages, many temperature steps."""
     eng, folder = engine_for(name, dtype)
     toks = tokens(305, vocab(name), 77)
-    ref = plain_logits(folder, toks)
-    s = eng.acquire()
-    eng.step([(s, toks[:5])], [[]])
-    got = [eng.step([(s, [toks[p]])], [[0]]) for p in range(5, 305)]
-    eng.release(s)
-    rows_agree(torch.cat(got), ref[5:], dtype, name)
+    got, ref = reference(eng, folder, toks, dtype, lambda: alone(eng, toks, 5))
+    rows_agree(got, ref, dtype, name)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -552,7 +665,11 @@ def test_trace_replay_as_a_process(dtype):
     folder = folder_for(name, TD[dtype])
     V = vocab(name)
     a, b = tokens(210, V, 5), tokens(33, V, 6)
-    refs = {"a": plain_logits(folder, a), "b": plain_logits(folder, b)}
+    if dtype == "float32":
+        refs = {"a": plain_logits(folder, a), "b": plain_logits(folder, b)}
+    else:
+        eng, _ = engine_for(name, dtype)
+        refs = {"a": alone(eng, a, 200).cpu(), "b": alone(eng, b, 30).cpu()}
     steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:200], "want": [0, 100, 199]},
                                      {"id": "b", "tokens": b[:30], "want": [29]}], "end": []}]
     for k in range(10):
