@@ -13,6 +13,7 @@
 // output's dtype.  One CTA per row with the row in registers (EPT values per thread); the
 // variance is taken from the deviations (two passes over registers), not from E[v^2].
 #include "common.cuh"
+#include <type_traits>
 
 namespace {
 
@@ -107,10 +108,165 @@ layer_norm_join_kernel(float* __restrict__ h, const TY* __restrict__ y, int n_sp
     }
 }
 
+// Many rows (prompts), 32-bit branch input, width a multiple of 4: GT threads share a row
+// (32: a warp per row and no block-wide barrier, for rows up to 2,048 values; 256: a CTA
+// per row, for wider ones), 16-byte loads issued up front, the row in registers.
+template <typename TX> struct LnPack4;
+template <> struct LnPack4<float> {
+    __device__ static void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct LnPack4<__nv_bfloat16> {
+    __device__ static void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<unsigned*>(&a);
+        u.y = *reinterpret_cast<unsigned*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
+template <int GT>
+__device__ __forceinline__ float group_sum(float v, float* red) {
+    if (GT == 32) return warp_sum(v);
+    return block_sum(v, red);
+}
+
+template <int NV, int GT>
+__device__ __forceinline__ void normalise4(float4 (&v)[NV], const NormSide& side, int H4, int H,
+                                           int lane, int rms, float* red) {
+    float mean = 0.f;
+    if (!rms) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        mean = group_sum<GT>(s, red) / (float)H;
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (lane + GT * i < H4) {
+            v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+            ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        }
+    }
+    const float r = 1.0f / sqrtf(group_sum<GT>(ss, red) / (float)H + side.eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int idx = lane + GT * i;
+        if (idx < H4) {
+            const float4 w = reinterpret_cast<const float4*>(side.w)[idx];
+            float4 b = make_float4(0, 0, 0, 0);
+            if (side.b) b = reinterpret_cast<const float4*>(side.b)[idx];
+            v[i].x = v[i].x * r * w.x + b.x; v[i].y = v[i].y * r * w.y + b.y;
+            v[i].z = v[i].z * r * w.z + b.z; v[i].w = v[i].w * r * w.w + b.w;
+        }
+    }
+}
+
+template <typename TX, int NV, int GT>
+__global__ void __launch_bounds__(GT == 32 ? 128 : 256)
+layer_norm_rows_kernel(float* __restrict__ h, const float* __restrict__ y, int n_splits,
+                       size_t split_stride, NormSide post, NormSide next, TX* __restrict__ x,
+                       int R, int H, float mult, int add_residual, int rms) {
+    pdl_wait();
+    pdl_launch_next();
+    __shared__ float red[33];
+    const int lane = GT == 32 ? (threadIdx.x & 31) : threadIdx.x;
+    const int row = GT == 32 ? blockIdx.x * 4 + (threadIdx.x >> 5) : blockIdx.x;
+    if (row >= R) return;                          // (whole warps, or nobody, leave)
+    const int H4 = H >> 2;
+    const size_t base = (size_t)row * H;
+    float4 v[NV];
+    if (y) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = lane + GT * i;
+            v[i] = idx < H4 ? reinterpret_cast<const float4*>(y + base)[idx]
+                            : make_float4(0, 0, 0, 0);
+        }
+        for (int s = 1; s < n_splits; ++s) {
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const int idx = lane + GT * i;
+                if (idx < H4) {
+                    const float4 t = reinterpret_cast<const float4*>(y + s * split_stride + base)[idx];
+                    v[i].x += t.x; v[i].y += t.y; v[i].z += t.z; v[i].w += t.w;
+                }
+            }
+        }
+        if (post.w) normalise4<NV, GT>(v, post, H4, H, lane, rms, red);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = lane + GT * i;
+            // (the stream's row is asked for here, not up front: with both in registers the
+            // widest rows spill, and a prompt has rows enough to hide the trip)
+            float4 hv = make_float4(0, 0, 0, 0);
+            if (add_residual && idx < H4) hv = reinterpret_cast<const float4*>(h + base)[idx];
+            v[i].x = v[i].x * mult + hv.x; v[i].y = v[i].y * mult + hv.y;
+            v[i].z = v[i].z * mult + hv.z; v[i].w = v[i].w * mult + hv.w;
+            if (idx >= H4) v[i] = make_float4(0, 0, 0, 0);
+            else if (add_residual) reinterpret_cast<float4*>(h + base)[idx] = v[i];
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = lane + GT * i;
+            v[i] = idx < H4 ? reinterpret_cast<const float4*>(h + base)[idx]
+                            : make_float4(0, 0, 0, 0);
+        }
+    }
+    if (next.w) normalise4<NV, GT>(v, next, H4, H, lane, rms, red);
+    if (x) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = lane + GT * i;
+            if (idx < H4) LnPack4<TX>::store(x + base + 4 * idx, v[i]);
+        }
+    }
+}
+
+template <typename TX>
+bool launch_layer_norm_rows(float* h, const float* y, int n_splits, size_t split_stride,
+                            NormSide post, NormSide next, TX* x, int R, int H, float mult,
+                            int add_residual, int rms, cudaStream_t stream) {
+#define AGV_LNR(NV, GT)                                                                         \
+    agv_launch(layer_norm_rows_kernel<TX, NV, GT>, (unsigned)(GT == 32 ? (R + 3) / 4 : R),      \
+               GT == 32 ? 128 : 256, 0, stream, h, y, n_splits, split_stride, post, next, x, R, \
+               H, mult, add_residual, rms)
+    if (H <= 2048) {
+        const int nv = (H / 4 + 31) / 32;
+        if (nv <= 2) AGV_LNR(2, 32);
+        else if (nv <= 4) AGV_LNR(4, 32);
+        else if (nv <= 8) AGV_LNR(8, 32);
+        else if (nv <= 12) AGV_LNR(12, 32);
+        else AGV_LNR(16, 32);
+    } else {
+        const int nv = (H / 4 + 255) / 256;
+        if (nv <= 4) AGV_LNR(4, 256);
+        else if (nv <= 8) AGV_LNR(8, 256);
+        else if (nv <= 16) AGV_LNR(16, 256);
+        else return false;
+    }
+#undef AGV_LNR
+    return true;
+}
+
 template <typename TY, typename TX>
 int launch_layer_norm(float* h, const void* y, int n_splits, size_t split_stride, NormSide post,
                       NormSide next, void* x, const int* rows, int R, int H, float mult,
                       int add_residual, int rms, cudaStream_t stream) {
+    if constexpr (std::is_same<TY, float>::value) {
+        // many rows of 32-bit input that move in 16-byte pieces
+        auto al = [](const void* p) { return !p || agv_aligned(p, 16); };
+        if (R > 64 && !rows && H % 4 == 0 && split_stride % 4 == 0 && al(h) && al(y) && al(x) &&
+            al(post.w) && al(post.b) && al(next.w) && al(next.b)) {
+            if (launch_layer_norm_rows<TX>(h, (const float*)y, n_splits, split_stride, post, next,
+                                           (TX*)x, R, H, mult, add_residual, rms, stream)) {
+                AGV_LAUNCH_OK("layer_norm_rows_kernel");
+                return 0;
+            }
+        }
+    }
     // about four values a thread, at most 1,024 threads
     int threads = ((H + 3) / 4 + 31) / 32 * 32;
     if (threads > 1024) threads = 1024;

@@ -33,34 +33,10 @@ __device__ __forceinline__ float moe_act(float t, int act) {
 constexpr int RT_WARPS = 4;
 constexpr int RT_MAX_E = 512;
 
-// One warp per token: logits by lanes over H, then lane 0 chooses.
-template <typename T>
-__global__ void __launch_bounds__(RT_WARPS * 32)
-moe_route_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ wr,
-                 const float* __restrict__ correction, int n_tokens, int H, int E, int n_groups,
-                 int keep, int top, int* __restrict__ ids, float* __restrict__ wts) {
-    pdl_wait();
-    pdl_launch_next();
-    extern __shared__ float smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * RT_WARPS + warp;
-    if (t >= n_tokens) return;
-    float* s = smem + (size_t)warp * 2 * E;      // sigmoid scores
-    float* c = s + E;                            // choice scores (consumed by the choice)
-    const T* xr = x + (size_t)t * ldx;
-    for (int e = 0; e < E; ++e) {
-        const T* w = wr + (size_t)e * H;
-        float z = 0.f;
-        for (int i = lane; i < H; i += 32) z = fmaf(to_f32(xr[i]), to_f32(w[i]), z);
-        z = warp_sum(z);
-        if (lane == 0) {
-            const float sg = 1.0f / (1.0f + expf(-z));
-            s[e] = sg;
-            c[e] = sg + (correction ? correction[e] : 0.f);
-        }
-    }
-    __syncwarp();
-    if (lane != 0) return;
+// The choice of one token from its scores (one thread): s [E] sigmoid scores, c [E] choice
+// scores (consumed).
+__device__ void moe_choose(float* s, float* c, int E, int n_groups, int keep, int top,
+                           int* __restrict__ ids, float* __restrict__ wts) {
     const int per = E / n_groups;
     if (keep < n_groups) {
         // group scores: the two largest choice scores of each group, summed
@@ -93,9 +69,182 @@ moe_route_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w
             if (v > best_v) { best = e; best_v = v; }
         }
         if (best < 0) best = 0;                 // (no finite score left: cannot happen with finite inputs)
-        ids[(size_t)t * top + k] = best;
-        wts[(size_t)t * top + k] = s[best];
+        ids[k] = best;
+        wts[k] = s[best];
         c[best] = -INFINITY;
+    }
+}
+
+// Index of the greatest of v[0..n) over a warp (the lowest index among equals; -1 if all are
+// minus infinity); every lane gets the result.
+__device__ __forceinline__ int warp_argmax(const float* v, int n, int lane) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = lane; i < n; i += 32) {
+        const float x = v[i];
+        if (x > bv) { bv = x; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    return bi == 0x7fffffff ? -1 : bi;
+}
+
+// The same choice made by a whole warp: gs [n_groups] is scratch for the group scores.
+__device__ void moe_choose_warp(float* s, float* c, float* gs, int E, int n_groups, int keep,
+                                int top, int* __restrict__ ids, float* __restrict__ wts,
+                                int lane) {
+    const int per = E / n_groups;
+    if (keep < n_groups) {
+        for (int g = lane; g < n_groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;              // largest, second largest
+            for (int i = 0; i < per; ++i) {
+                const float v = c[g * per + i];
+                if (v > a) { b = a; a = v; }
+                else if (v > b) b = v;
+            }
+            gs[g] = per > 1 ? a + b : a;
+        }
+        __syncwarp();
+        // a kept group's score becomes "not a number", which is never the greatest again;
+        // the groups that still hold a number afterwards are dropped
+        for (int k = 0; k < keep; ++k) {
+            int best = warp_argmax(gs, n_groups, lane);
+            if (best < 0) {
+                // (only groups of minus infinity left: take the first not yet kept)
+                best = 0;
+                while (best < n_groups - 1 && gs[best] != gs[best]) ++best;
+            }
+            __syncwarp();
+            if (lane == 0) gs[best] = NAN;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (gs[e / per] == gs[e / per]) c[e] = -INFINITY;    // not marked: dropped
+        __syncwarp();
+    }
+    for (int k = 0; k < top; ++k) {
+        int best = warp_argmax(c, E, lane);
+        if (best < 0) best = 0;                 // (no finite score left: cannot happen with finite inputs)
+        __syncwarp();
+        if (lane == 0) {
+            ids[k] = best;
+            wts[k] = s[best];
+            c[best] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
+// One warp per token: logits by lanes over H, then lane 0 chooses.  The general form (any
+// H, any alignment).
+template <typename T>
+__global__ void __launch_bounds__(RT_WARPS * 32)
+moe_route_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ wr,
+                 const float* __restrict__ correction, int n_tokens, int H, int E, int n_groups,
+                 int keep, int top, int* __restrict__ ids, float* __restrict__ wts) {
+    pdl_wait();
+    pdl_launch_next();
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * RT_WARPS + warp;
+    if (t >= n_tokens) return;
+    float* s = smem + (size_t)warp * 2 * E;      // sigmoid scores
+    float* c = s + E;                            // choice scores (consumed by the choice)
+    const T* xr = x + (size_t)t * ldx;
+    for (int e = 0; e < E; ++e) {
+        const T* w = wr + (size_t)e * H;
+        float z = 0.f;
+        for (int i = lane; i < H; i += 32) z = fmaf(to_f32(xr[i]), to_f32(w[i]), z);
+        z = warp_sum(z);
+        if (lane == 0) {
+            const float sg = 1.0f / (1.0f + expf(-z));
+            s[e] = sg;
+            c[e] = sg + (correction ? correction[e] : 0.f);
+        }
+    }
+    __syncwarp();
+    if (lane == 0)
+        moe_choose(s, c, E, n_groups, keep, top, ids + (size_t)t * top, wts + (size_t)t * top);
+}
+
+// 16 bytes of a row as 32-bit values.
+template <typename T> struct Row16;
+template <> struct Row16<float> {
+    static constexpr int N = 4;
+    __device__ static void load(const float* p, float (&v)[4]) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+    }
+};
+template <> struct Row16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    __device__ static void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const unsigned u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(u[i] << 16);
+            v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+        }
+    }
+};
+
+// The same for rows that move in 16-byte pieces: a CTA of RT_VW warps takes RT_TOK tokens,
+// warp w the experts w, w + RT_VW, ...; a lane's piece of a router row meets the same piece
+// of every token of the CTA, so the router's matrix is read once per RT_TOK tokens, and the
+// loads of a row are independent of one another.  Then warp t chooses for token t.  Few
+// tokens (decoding) take a CTA of sixteen warps each, many (prompts) share CTAs of eight by
+// fours.
+template <typename T, int RT_TOK, int RT_VW>
+__global__ void __launch_bounds__(RT_VW * 32)
+moe_route_tiled_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ wr,
+                       const float* __restrict__ correction, int n_tokens, int H, int E,
+                       int n_groups, int keep, int top, int* __restrict__ ids,
+                       float* __restrict__ wts) {
+    pdl_wait();
+    pdl_launch_next();
+    extern __shared__ float smem[];              // [RT_TOK][3][E]
+    constexpr int N = Row16<T>::N;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.x * RT_TOK;
+    const int pieces = H / N;
+    const T* xr[RT_TOK];
+#pragma unroll
+    for (int k = 0; k < RT_TOK; ++k) xr[k] = x + (size_t)min(t0 + k, n_tokens - 1) * ldx;
+    for (int e = warp; e < E; e += RT_VW) {
+        const T* w = wr + (size_t)e * H;
+        float z[RT_TOK] = {};
+#pragma unroll 4
+        for (int i = lane; i < pieces; i += 32) {
+            float wv[N], xv[N];
+            Row16<T>::load(w + i * N, wv);
+#pragma unroll
+            for (int k = 0; k < RT_TOK; ++k) {
+                Row16<T>::load(xr[k] + i * N, xv);
+#pragma unroll
+                for (int j = 0; j < N; ++j) z[k] = fmaf(xv[j], wv[j], z[k]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < RT_TOK; ++k) {
+            const float zz = warp_sum(z[k]);
+            if (lane == 0) {
+                const float sg = 1.0f / (1.0f + expf(-zz));
+                smem[(k * 3) * E + e] = sg;
+                smem[(k * 3 + 1) * E + e] = sg + (correction ? correction[e] : 0.f);
+            }
+        }
+    }
+    __syncthreads();
+    if (warp < RT_TOK && t0 + warp < n_tokens) {
+        const int t = t0 + warp;
+        moe_choose_warp(smem + (warp * 3) * E, smem + (warp * 3 + 1) * E,
+                        smem + (warp * 3 + 2) * E, E, n_groups, keep, top, ids + (size_t)t * top,
+                        wts + (size_t)t * top, lane);
     }
 }
 
@@ -160,7 +309,7 @@ moe_plan_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int 
 
 constexpr int GM = 64, GN = 64, GK = 16;
 
-// A tile of 64 sorted rows x 64 output features of one expert.  A rows are gathered through
+// 64 sorted rows x 64 output features of one expert (sub of these to a tile of the plan).  A rows are gathered through
 // a_index (null: row = pos, live where tok[pos] >= 0); C rows go to c_index[pos] (null:
 // pos) times c_scale[pos] (null: 1).
 template <typename TA, typename TW, typename TO, bool GATED>
@@ -169,10 +318,10 @@ moe_grouped_kernel(const TA* __restrict__ A, long long lda, const int* __restric
                    const int* __restrict__ tok, const TW* __restrict__ W,
                    const TW* __restrict__ W2, TO* __restrict__ C, long long ldc,
                    const int* __restrict__ c_index, const float* __restrict__ c_scale,
-                   const int* __restrict__ tile_e, int N, int K, int act) {
+                   const int* __restrict__ tile_e, int N, int K, int act, int sub) {
     pdl_wait();
     pdl_launch_next();
-    const int e = tile_e[blockIdx.y];
+    const int e = tile_e[blockIdx.y / sub];
     if (e < 0) return;
     __shared__ float As[GK][GM + 4];
     __shared__ float Ws[GK][GN + 4];
@@ -259,6 +408,24 @@ AGV_API int agv_moe_route(const void* x, long long ldx, const void* wr, const fl
                 "groups kept", top, keep * (E / n_groups));
     AGV_REQUIRE(ldx >= H, "moe_route: row stride shorter than a row");
     if (T == 0) return 0;
+    const int piece = dtype == AGV_F32 ? 4 : 8;
+    if (H % piece == 0 && ldx % piece == 0 && agv_aligned(x, 16) && agv_aligned(wr, 16)) {
+        AGV_REQUIRE(dtype == AGV_F32 || dtype == AGV_BF16, "moe_route: unknown dtype %d", dtype);
+#define AGV_ROUTE(TT, TOK, VW)                                                                  \
+    agv_launch(moe_route_tiled_kernel<TT, TOK, VW>, (unsigned)((T + TOK - 1) / TOK), VW * 32,   \
+               (size_t)TOK * 3 * E * sizeof(float), stream, (const TT*)x, ldx, (const TT*)wr,   \
+               correction, T, H, E, n_groups, keep, top, ids, wts)
+        if (T <= 64) {
+            if (dtype == AGV_F32) AGV_ROUTE(float, 1, 16);
+            else AGV_ROUTE(__nv_bfloat16, 1, 16);
+        } else {
+            if (dtype == AGV_F32) AGV_ROUTE(float, 4, 8);
+            else AGV_ROUTE(__nv_bfloat16, 4, 8);
+        }
+#undef AGV_ROUTE
+        AGV_LAUNCH_OK("moe_route_tiled_kernel");
+        return 0;
+    }
     const unsigned grid = (unsigned)((T + RT_WARPS - 1) / RT_WARPS);
     const size_t smem = (size_t)RT_WARPS * 2 * E * sizeof(float);
     if (dtype == AGV_F32)
@@ -274,36 +441,45 @@ AGV_API int agv_moe_route(const void* x, long long ldx, const void* wr, const fl
     return 0;
 }
 
-AGV_API int agv_moe_tile_rows() { return GM; }
-
-// Upper bounds the caller sizes the plan's arrays with.
-AGV_API int agv_moe_plan_tiles(int T, int top, int E) { return (T * top + GM - 1) / GM + E; }
-AGV_API int agv_moe_plan_rows(int T, int top, int E) { return agv_moe_plan_tiles(T, top, E) * GM; }
+// Upper bounds the caller sizes the plan's arrays with; tile: rows per tile (a multiple of 64).
+AGV_API int agv_moe_plan_tiles(int T, int top, int E, int tile) {
+    return (T * top + tile - 1) / tile + E;
+}
+AGV_API int agv_moe_plan_rows(int T, int top, int E, int tile) {
+    return agv_moe_plan_tiles(T, top, E, tile) * tile;
+}
 
 // See moe_plan_kernel; tok, dst, wpos: [agv_moe_plan_rows], pos_of: [T * top],
 // tile_e: [agv_moe_plan_tiles].
-AGV_API int agv_moe_plan(const int* ids, const float* wts, int T, int top, int E, int* tok,
-                         int* dst, float* wpos, int* pos_of, int* tile_e, cudaStream_t stream) {
+AGV_API int agv_moe_plan(const int* ids, const float* wts, int T, int top, int E, int tile,
+                         int* tok, int* dst, float* wpos, int* pos_of, int* tile_e,
+                         cudaStream_t stream) {
     AGV_REQUIRE(T >= 0 && top > 0 && E > 0, "moe_plan: bad sizes");
+    AGV_REQUIRE(tile >= GM && tile % GM == 0, "moe_plan: tiles of %d rows (a multiple of %d)", tile, GM);
     AGV_REQUIRE(E <= 4096, "moe_plan: %d experts exceed 4096", E);
     if (T == 0) return 0;
     const size_t smem = (size_t)(2 * E + 1) * sizeof(int);
-    agv_launch(moe_plan_kernel, 1u, 1024, smem, stream, ids, wts, T, top, E, GM, tok, dst, wpos,
-               pos_of, tile_e, agv_moe_plan_rows(T, top, E), agv_moe_plan_tiles(T, top, E));
+    agv_launch(moe_plan_kernel, 1u, 1024, smem, stream, ids, wts, T, top, E, tile, tok, dst, wpos,
+               pos_of, tile_e, agv_moe_plan_rows(T, top, E, tile),
+               agv_moe_plan_tiles(T, top, E, tile));
     AGV_LAUNCH_OK("moe_plan_kernel");
     return 0;
 }
 
 // The grouped product over a plan.  a: rows of stride lda (a_index null: row = sorted
-// position); w (and w2 for the gated form): [E, N, K] dense; c: rows of stride ldc at
+// position); tile: the plan's rows per tile; w (and w2 for the gated form): [E, N, K] dense; c: rows of stride ldc at
 // c_index[pos] (null: pos), times c_scale[pos] (null: 1).  in_dtype: a and the weights;
 // out_dtype: c.
 AGV_API int agv_moe_grouped(const void* a, long long lda, const int* a_index, const int* tok,
                             const void* w, const void* w2, void* c, long long ldc,
                             const int* c_index, const float* c_scale, const int* tile_e,
-                            int n_tiles, int N, int K, int in_dtype, int out_dtype, int act,
-                            cudaStream_t stream) {
+                            int n_tiles, int tile, int N, int K, int in_dtype, int out_dtype,
+                            int act, cudaStream_t stream) {
     AGV_REQUIRE(n_tiles >= 0 && N > 0 && K > 0, "moe_grouped: bad sizes");
+    AGV_REQUIRE(tile >= GM && tile % GM == 0, "moe_grouped: tiles of %d rows (a multiple of %d)",
+                tile, GM);
+    const int sub = tile / GM;
+    n_tiles *= sub;
     AGV_REQUIRE(lda >= K && ldc >= N, "moe_grouped: row strides shorter than rows");
     AGV_REQUIRE(n_tiles <= 65535, "moe_grouped: %d tiles exceed the grid limit", n_tiles);
     if (n_tiles == 0) return 0;
@@ -313,11 +489,11 @@ AGV_API int agv_moe_grouped(const void* a, long long lda, const int* a_index, co
         if (w2)                                                                                  \
             agv_launch(moe_grouped_kernel<TA, TA, TO, true>, grid, 256, 0, stream, (const TA*)a, \
                        lda, a_index, tok, (const TA*)w, (const TA*)w2, (TO*)c, ldc, c_index,     \
-                       c_scale, tile_e, N, K, act);                                              \
+                       c_scale, tile_e, N, K, act, sub);                                         \
         else                                                                                     \
             agv_launch(moe_grouped_kernel<TA, TA, TO, false>, grid, 256, 0, stream,              \
                        (const TA*)a, lda, a_index, tok, (const TA*)w, (const TA*)nullptr,        \
-                       (TO*)c, ldc, c_index, c_scale, tile_e, N, K, act);                        \
+                       (TO*)c, ldc, c_index, c_scale, tile_e, N, K, act, sub);                   \
     } while (0)
     if (in_dtype == AGV_F32 && out_dtype == AGV_F32) AGV_MOE(float, float);
     else if (in_dtype == AGV_BF16 && out_dtype == AGV_BF16) AGV_MOE(__nv_bfloat16, __nv_bfloat16);

@@ -1,11 +1,14 @@
 // The experts' grouped products in bfloat16 on the tensor cores (tcgen05 + TMA), over the
-// plan that moe.cu makes: a tile of 64 sorted (token, choice) rows belongs to one expert.
+// plan that moe.cu makes: a tile of sorted (token, choice) rows belongs to one expert.
 //
-// One CTA per (128 weight rows of the tile's expert, 64 sorted rows).  The weight rows
+// One CTA per (128 weight rows of the tile's expert, one tile of 64 or 128 sorted rows: the
+// plan's tile; 128 where experts have rows enough, since a product of N 128 feeds the
+// tensor pipe with half the bytes per flop of one of N 64).  The weight rows
 // are the M side (the experts' matrices are stacked [E * N, K], so an expert is a row
-// offset in one tensor map), the 64 rows the N side; both come by TMA with the 128-byte
+// offset in one tensor map), the tile's rows the N side; both come by TMA with the 128-byte
 // swizzle into a ring of stages, the products accumulate in tensor memory, and four
-// warps read the accumulator back, one output feature per thread:
+// warps read the accumulator back, one output feature per thread, and pass the tile
+// through shared memory so that rows leave in 16-byte pieces:
 //   gated:  z[pos, f] = act(gate) * up, two accumulators side by side, bfloat16 out;
 //   plain:  out[dst[pos], f] = w[pos] * acc, 32-bit out (the down product, scattered to
 //           [choice, token] and scaled by the pair's weight).
@@ -17,25 +20,28 @@
 // requested before the wait for the kernels before; every wait on a barrier is bounded
 // and leaves a code for agv_moe_tc_status.
 #include "tcgen05.cuh"
+#include <type_traits>
 
 namespace {
 using namespace tc5;
 
 constexpr int MT_M = 128;          // weight rows per CTA
-constexpr int MT_N = 64;           // sorted rows per CTA (the plan's tile)
 constexpr int MT_K = 64;           // 64 bf16 = one 128-byte swizzle row
 constexpr int MT_THREADS = 192;
-constexpr int MT_STAGES = 4;
 
 __device__ int g_moe_status = 0;   // 0 ok; else (role << 8) | stage of the first wait that gave up
 
-template <bool GATED>
+template <bool GATED, int MT_N>
 struct MTile {
+    // The plain form (the down product: a short K, a large 32-bit tile to write) keeps its
+    // ring small enough for two CTAs to share an SM, so that one's epilogue runs under the
+    // other's products; the gated form has a long K and takes the SM alone.
+    static constexpr int STAGES = GATED ? 4 : 3;
     static constexpr int A_BYTES = MT_M * MT_K * 2;
     static constexpr int B_BYTES = MT_N * MT_K * 2;
     static constexpr int STAGE_BYTES = A_BYTES * (GATED ? 2 : 1) + B_BYTES;
     static constexpr int TMEM_COLS = GATED ? 2 * MT_N : MT_N;
-    static constexpr int SMEM = MT_STAGES * STAGE_BYTES + 1024 /*align*/ + 1024 /*barriers, rows*/;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 2048 /*barriers, rows*/;
 };
 
 __device__ __forceinline__ float mt_act(float t, int act) {
@@ -46,8 +52,8 @@ __device__ __forceinline__ float mt_act(float t, int act) {
     return 0.5f * t * (1.0f + th);
 }
 
-template <bool GATED>
-__global__ void __launch_bounds__(MT_THREADS, 1)
+template <bool GATED, int MT_N>
+__global__ void __launch_bounds__(MT_THREADS, GATED ? 1 : 2)
 moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                       const __grid_constant__ CUtensorMap map_w2,
                       const __grid_constant__ CUtensorMap map_a, void* __restrict__ out,
@@ -58,7 +64,8 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w,
     pdl_wait();                                    // the plan is the work of kernels before
     const int e = tile_e[blockIdx.y];
     if (e < 0) return;
-    using TL = MTile<GATED>;
+    using TL = MTile<GATED, MT_N>;
+    constexpr int MT_STAGES = TL::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(smem + MT_STAGES * TL::STAGE_BYTES);
@@ -66,9 +73,9 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w,
     uint64_t* acc_full = empty + MT_STAGES;
     uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    int* s_tok = (int*)(tmem_slot + 4);            // [64] token of each row, -1: padding
-    int* s_row = s_tok + MT_N;                     // [64] output row
-    float* s_scale = (float*)(s_row + MT_N);       // [64]
+    int* s_tok = (int*)(tmem_slot + 4);            // [MT_N] token of each row, -1: padding
+    int* s_row = s_tok + MT_N;                     // [MT_N] output row
+    float* s_scale = (float*)(s_row + MT_N);       // [MT_N]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * MT_M;              // first output feature
@@ -161,7 +168,6 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w,
     } else if (warp >= 2) {
         // ------------------------------------------------------------ epilogue
         const int quarter = warp & 3;      // the tensor-memory lanes this warp may read
-        const int f = m0 + quarter * 32 + lane;
         bool ok = mbar_wait(acc_full, 0);
         if (!ok) {
             atomicCAS(&g_moe_status, 0, (3 << 8));
@@ -170,6 +176,13 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w,
         tc_fence_after();
         const bool run = ok && !*abort_flag;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        // The tile goes through shared memory (the ring of stages is free once the
+        // accumulator is complete) so that a row leaves in 16-byte pieces: [row][128 features].
+        using TO = typename std::conditional<GATED, __nv_bfloat16, float>::type;
+        static_assert(MT_N * MT_M * (int)sizeof(TO) <= MT_STAGES * TL::STAGE_BYTES,
+                      "the output tile must fit the ring of stages");
+        TO* ctile = (TO*)smem;
+        const int fl = quarter * 32 + lane;
         if (run) {
 #pragma unroll 1
             for (int c = 0; c < MT_N; c += 16) {
@@ -177,19 +190,36 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                 tc_ld16(lane_base + c, r);
                 if (GATED) tc_ld16(lane_base + MT_N + c, u);
                 tc_wait_ld();
-                if (f < N) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (s_tok[c + j] < 0) continue;
-                        const size_t at = (size_t)s_row[c + j] * ldc + f;
-                        float v = __uint_as_float(r[j]);
-                        if (GATED) {
-                            v = mt_act(v, act) * __uint_as_float(u[j]);
-                            ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(v);
-                        } else {
-                            ((float*)out)[at] = v * s_scale[c + j];
-                        }
+                for (int j = 0; j < 16; ++j) {
+                    float v = __uint_as_float(r[j]);
+                    if constexpr (GATED) {
+                        v = mt_act(v, act) * __uint_as_float(u[j]);
+                        ctile[(c + j) * MT_M + fl] = __float2bfloat16_rn(v);
+                    } else {
+                        ctile[(c + j) * MT_M + fl] = v * s_scale[c + j];
                     }
+                }
+            }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps
+        if (run) {
+            constexpr int EPV = 16 / (int)sizeof(TO);          // elements per 16 bytes
+            constexpr int VPR = MT_M / EPV;                    // 16-byte pieces per row
+            const int et = (warp - 2) * 32 + lane;
+            TO* obase = (TO*)out + m0;
+            const bool fast = m0 + MT_M <= N && ldc % EPV == 0 && ((uintptr_t)obase & 15) == 0;
+            if (fast) {
+                for (int i = et; i < MT_N * VPR; i += 128) {
+                    const int n = i / VPR, vi = i % VPR;
+                    if (s_tok[n] < 0) continue;
+                    *reinterpret_cast<uint4*>(obase + (size_t)s_row[n] * ldc + vi * EPV) =
+                        reinterpret_cast<const uint4*>(ctile)[i];
+                }
+            } else {
+                for (int i = et; i < MT_N * MT_M; i += 128) {
+                    const int n = i / MT_M, f2 = i % MT_M;
+                    if (s_tok[n] >= 0 && m0 + f2 < N) obase[(size_t)s_row[n] * ldc + f2] = ctile[i];
                 }
             }
         }
@@ -268,12 +298,14 @@ AGV_API int agv_moe_gather_rows(const void* x, long long ldx, const int* tok, vo
 // a: [rows, K] bfloat16 in sorted order (row stride lda); w (and w2 for the gated form):
 // [E, N, K] bfloat16 dense; tok, tile_e: the plan.  Gated: c [rows, N] bfloat16 rows of stride
 // ldc at the sorted positions.  Plain: c 32-bit, row c_index[pos] (null: pos) times
-// c_scale[pos] (null: 1).
+// c_scale[pos] (null: 1).  tile: the plan's rows per tile, 64 or 128.
 AGV_API int agv_moe_grouped_tc(const void* a, long long lda, int rows, const int* tok,
                                const void* w, const void* w2, int E, void* c, long long ldc,
                                const int* c_index, const float* c_scale, const int* tile_e,
-                               int n_tiles, int N, int K, int act, cudaStream_t stream) {
-    AGV_REQUIRE(n_tiles >= 0 && E > 0 && rows >= n_tiles * MT_N, "moe_grouped_tc: bad sizes");
+                               int n_tiles, int tile, int N, int K, int act,
+                               cudaStream_t stream) {
+    AGV_REQUIRE(tile == 64 || tile == 128, "moe_grouped_tc: tiles of %d rows (64 or 128)", tile);
+    AGV_REQUIRE(n_tiles >= 0 && E > 0 && rows >= n_tiles * tile, "moe_grouped_tc: bad sizes");
     AGV_REQUIRE(agv_moe_grouped_tc_supported(N, K, lda), "moe_grouped_tc: K (%d) and the row "
                 "stride (%lld) must be multiples of 8", K, lda);
     AGV_REQUIRE(agv_aligned(a, 16) && agv_aligned(w, 16) && agv_aligned(w2, 16),
@@ -288,29 +320,25 @@ AGV_API int agv_moe_grouped_tc(const void* a, long long lda, int rows, const int
     } else {
         mw2 = mw;
     }
-    if (int rc = mt_map(&ma, a, rows, K, lda, MT_N)) return rc;
+    if (int rc = mt_map(&ma, a, rows, K, lda, tile)) return rc;
     dim3 grid((N + MT_M - 1) / MT_M, n_tiles);
-    if (w2) {
-        auto kern = moe_grouped_tc_kernel<true>;
-        static bool configured = false;
-        if (!configured) {
-            AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             MTile<true>::SMEM));
-            configured = true;
-        }
-        agv_launch(kern, grid, MT_THREADS, MTile<true>::SMEM, stream, mw, mw2, ma, c, ldc, tok,
-                   c_index, c_scale, tile_e, N, K, act);
-    } else {
-        auto kern = moe_grouped_tc_kernel<false>;
-        static bool configured = false;
-        if (!configured) {
-            AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             MTile<false>::SMEM));
-            configured = true;
-        }
-        agv_launch(kern, grid, MT_THREADS, MTile<false>::SMEM, stream, mw, mw2, ma, c, ldc, tok,
-                   c_index, c_scale, tile_e, N, K, act);
-    }
+#define AGV_MT(GATED, BN)                                                                       \
+    do {                                                                                        \
+        auto kern = moe_grouped_tc_kernel<GATED, BN>;                                           \
+        static bool configured = false;                                                         \
+        if (!configured) {                                                                      \
+            AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                             MTile<GATED, BN>::SMEM));                          \
+            configured = true;                                                                  \
+        }                                                                                       \
+        agv_launch(kern, grid, MT_THREADS, MTile<GATED, BN>::SMEM, stream, mw, mw2, ma, c, ldc, \
+                   tok, c_index, c_scale, tile_e, N, K, act);                                   \
+    } while (0)
+    if (w2 && tile == 128) AGV_MT(true, 128);
+    else if (w2) AGV_MT(true, 64);
+    else if (tile == 128) AGV_MT(false, 128);
+    else AGV_MT(false, 64);
+#undef AGV_MT
     AGV_LAUNCH_OK("moe_grouped_tc_kernel");
     return 0;
 }

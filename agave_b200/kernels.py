@@ -268,23 +268,26 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
 class MoePlan:
     """Where the (token, choice) pairs of a step lie once sorted by expert (device arrays;
     see ``csrc/moe.cu``)."""
-    __slots__ = ("T", "top", "E", "rows", "tiles", "tok", "dst", "wpos", "pos_of", "tile_e")
+    __slots__ = ("T", "top", "E", "tile", "rows", "tiles", "tok", "dst", "wpos", "pos_of", "tile_e")
 
 
-def moe_plan(ids: torch.Tensor, wts: torch.Tensor, n_experts: int) -> MoePlan:
+def moe_plan(ids: torch.Tensor, wts: torch.Tensor, n_experts: int, tile: int = 0) -> MoePlan:
+    """``tile``: rows per tile, 64 or 128 (0: 128 where an expert gets some hundred rows on
+    average, so that padding every expert's run to the tile costs little, else 64)."""
     T, top = ids.shape
     lib = library()
     p = MoePlan()
     p.T, p.top, p.E = T, top, n_experts
-    p.rows = lib.agv_moe_plan_rows(T, top, n_experts)
-    p.tiles = lib.agv_moe_plan_tiles(T, top, n_experts)
+    p.tile = tile or (128 if T * top >= 96 * n_experts else 64)
+    p.rows = lib.agv_moe_plan_rows(T, top, n_experts, p.tile)
+    p.tiles = lib.agv_moe_plan_tiles(T, top, n_experts, p.tile)
     dev = ids.device
     ints = torch.empty(2 * p.rows + T * top + p.tiles, dtype=torch.int32, device=dev)
     p.tok, p.dst = ints[:p.rows], ints[p.rows:2 * p.rows]
     p.pos_of = ints[2 * p.rows:2 * p.rows + T * top]
     p.tile_e = ints[2 * p.rows + T * top:]
     p.wpos = torch.empty(p.rows, dtype=torch.float32, device=dev)
-    _check(lib.agv_moe_plan(_ptr(ids), _ptr(wts), T, top, n_experts, _ptr(p.tok), _ptr(p.dst),
+    _check(lib.agv_moe_plan(_ptr(ids), _ptr(wts), T, top, n_experts, p.tile, _ptr(p.tok), _ptr(p.dst),
                             _ptr(p.wpos), _ptr(p.pos_of), _ptr(p.tile_e), _stream()))
     return p
 
@@ -311,8 +314,8 @@ def moe_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: MoePl
             _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(plan.tok) if gather else None,
             _ptr(plan.tok), _ptr(w), _ptr(w2), _ptr(out), ctypes.c_longlong(out.stride(0)),
             _ptr(plan.dst) if scatter else None, _ptr(plan.wpos) if scatter else None,
-            _ptr(plan.tile_e), plan.tiles, N, K, dtype_code(a.dtype), dtype_code(out.dtype),
-            ACT[activation], _stream()))
+            _ptr(plan.tile_e), plan.tiles, plan.tile, N, K, dtype_code(a.dtype),
+            dtype_code(out.dtype), ACT[activation], _stream()))
 
 
 def moe_grouped_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -360,7 +363,7 @@ def moe_grouped_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: Mo
         _check(library().agv_moe_grouped_tc(
             _ptr(a), ctypes.c_longlong(a.stride(0)), plan.rows, _ptr(plan.tok), _ptr(w), _ptr(w2),
             E, _ptr(out), ctypes.c_longlong(out.stride(0)), _ptr(plan.dst) if scatter else None,
-            _ptr(plan.wpos) if scatter else None, _ptr(plan.tile_e), plan.tiles, N, K,
+            _ptr(plan.wpos) if scatter else None, _ptr(plan.tile_e), plan.tiles, plan.tile, N, K,
             ACT[activation], _stream()))
 
 

@@ -309,15 +309,43 @@ def run_compare(args):
                         engine.release(slot)
                 else:
                     slots = [engine.acquire() for _ in range(batch)]
-                    engine.step([(s, prompt[:ctx_len]) for s in slots], [[] for _ in slots])
+                    engine.step([(s, prompt[:ctx_len - 7 * i]) for i, s in enumerate(slots)],
+                                [[] for _ in slots])
+                    chosen = []                    # the experts each routed layer picks (device)
+                    routed = [b.ffn for b in engine.model.blocks
+                              if getattr(b, "ffn", None) is not None and hasattr(b.ffn, "route")]
+                    for ffn in routed:
+                        def route(x, _r=ffn.route):
+                            ids, wts = _r(x)
+                            chosen.append(ids)
+                            return ids, wts
+                        ffn.route = route
                     for rep in range(3):
                         if rep == 2:
+                            del chosen[:]
                             counters.__enter__()
-                        engine.step([(s, [5 + rep]) for s in slots], [[0] for _ in slots])
+                        engine.step([(s, [5 + rep + i]) for i, s in enumerate(slots)],
+                                    [[0] for _ in slots])
+                    for ffn in routed:
+                        del ffn.route                # back to the class's method
                     for s in slots:
                         engine.release(s)
                 table = counters.table()
                 counters.__exit__()
+                if what == "decode" and chosen:
+                    # a decode step reads only the experts some token chose: the spans' byte
+                    # counts assume min(experts, pairs) of them, the truth is counted here
+                    used = sum(int(c.unique().numel()) for c in chosen) / len(chosen)
+                    E = routed[0].spec.n_experts
+                    assumed = min(E, batch * routed[0].spec.top)
+                    for op in ("experts_gate_up", "experts_down"):
+                        if op in table:
+                            table[op]["bytes"] = int(table[op]["bytes"] * used / assumed)
+                    entry_extra = {"experts_read_per_layer": round(used, 1), "experts": E}
+                else:
+                    entry_extra = {}
+                if what == "decode":
+                    decode_extra = entry_extra
                 rows = {}
                 for op, r in table.items():
                     sec = r["total_us"] * 1e-6
@@ -332,7 +360,8 @@ def run_compare(args):
                            "decode_ms_per_step": round(ms, 4),
                            "decode_tokens_per_s": round(batch / ms * 1e3, 1),
                            "kernels_per_decode_step": launches,
-                           "weight_gb": round(engine.model.weight_bytes() / 1e9, 3), "ops": ops}
+                           "weight_gb": round(engine.model.weight_bytes() / 1e9, 3), "ops": ops,
+                           **decode_extra}
             del engine
             torch.cuda.empty_cache()
         out["sizes"][size] = entry
