@@ -36,7 +36,7 @@ struct MTile {
     // The plain form (the down product: a short K, a large 32-bit tile to write) keeps its
     // ring small enough for two CTAs to share an SM, so that one's epilogue runs under the
     // other's products; the gated form has a long K and takes the SM alone.
-    static constexpr int STAGES = GATED ? 4 : 3;
+    static constexpr int STAGES = GATED ? (MT_N == 128 ? 2 : 4) : 3;
     static constexpr int A_BYTES = MT_M * MT_K * 2;
     static constexpr int B_BYTES = MT_N * MT_K * 2;
     static constexpr int STAGE_BYTES = A_BYTES * (GATED ? 2 : 1) + B_BYTES;
@@ -53,7 +53,7 @@ __device__ __forceinline__ float mt_act(float t, int act) {
 }
 
 template <bool GATED, int MT_N>
-__global__ void __launch_bounds__(MT_THREADS, GATED ? 1 : 2)
+__global__ void __launch_bounds__(MT_THREADS, (GATED && MT_N != 128) ? 1 : 2)
 moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                       const __grid_constant__ CUtensorMap map_w2,
                       const __grid_constant__ CUtensorMap map_a, void* __restrict__ out,

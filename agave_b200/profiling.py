@@ -35,6 +35,9 @@ Cases (Gemma 3 1B layer sizes, random bfloat16 data):
   decode_step_4b, decode_step_27b   the same with the layer sizes of the 4B model (batch 8,
                        256..4,096 positions) and the 27B model (batch 16, 2,048 positions)
   prefill_step         whole prompt steps of the same model, one prompt of 2,048 tokens
+  experts_prefill, experts_decode   a routed feed-forward (width 2,048, 32 experts of width
+                       768 in 8 groups, 4 of them a token, 4 groups kept): router, plan, gather
+                       and the two grouped products, for 2,048 tokens and for 8
 
 Each case prints the mean time per call: the calls run back to back from a CUDA
 graph, each on the next of several copies of its operands, the copies together
@@ -330,7 +333,31 @@ def case_decode_step(batch=8, sizes="1b", lo=128, hi=2048):
     return (lambda i: eng.step([(s, [5]) for s in slots], [[0]] * batch)), 0, 0, 0
 
 
+def case_experts(T):
+    """A routed feed-forward's whole forward pass (its 300 MB of experts are larger than L2)."""
+    from .config.base import RoutedFeedForwardSpec
+    from .parts.moe import RoutedFeedForward
+    h, ff, E, top = 2048, 768, 32, 4
+    spec = RoutedFeedForwardSpec(n_experts=E, top=top, intermediate_size=ff, n_groups=8,
+                                 keep_groups=4)
+    t = {"router.weight": _rnd(E, h, scale=2.0 / h ** 0.5),
+         "router.correction": torch.randn(E, device=DEV) * 0.3}
+    for e in range(E):
+        t[f"experts.{e}.gate_proj.weight"] = _rnd(ff, h, scale=0.02)
+        t[f"experts.{e}.up_proj.weight"] = _rnd(ff, h, scale=0.02)
+        t[f"experts.{e}.down_proj.weight"] = _rnd(h, ff, scale=0.02)
+    part = RoutedFeedForward(spec, h, torch.bfloat16, torch.device(DEV))
+    part.load(t, torch.bfloat16, torch.device(DEV))
+    del t
+    x = _rnd(T, h)
+    used = min(E, T * top)
+    nbytes = used * 3 * h * ff * 2 + T * h * 2 + top * T * h * 4
+    return (lambda i: part.forward(x, None)), 6 * T * top * h * ff, nbytes, 1
+
+
 CASES = {
+    "experts_prefill": lambda: case_experts(2048),
+    "experts_decode": lambda: case_experts(8),
     "gemm_gated_prefill": lambda: case_gemm_gated(2048),
     "gemm_down_prefill": lambda: case_gemm_down(2048),
     "gemm_gated_decode": lambda: case_gemm_gated(8),
