@@ -702,3 +702,29 @@ def test_trace_replay_as_a_process(dtype):
     rows_agree(torch.cat(rows), torch.cat(want), dtype, "decoded")
     import shutil
     shutil.rmtree(out, ignore_errors=True)
+
+
+def test_trace_replay_counts_tokens_not_pages():
+    """--max-tokens counts the tokens live requests hold, without the padding of the
+    cache's pages: a dozen requests of two or three tokens each fit a budget of 36."""
+    name = "R1"
+    folder = folder_for(name, torch.float32)
+    V = vocab(name)
+    seqs = {f"q{i}": tokens(3, V, 700 + i) for i in range(12)}
+    steps = [{"step": 0, "entries": [{"id": k, "tokens": s[:2], "want": [1]}
+                                     for k, s in seqs.items()], "end": []},
+             {"step": 1, "entries": [{"id": k, "tokens": s[2:], "want": [0]}
+                                     for k, s in seqs.items()], "end": list(seqs)}]
+    out = tempfile.mkdtemp(prefix="ramilorn_trace_")
+    text = "".join(json.dumps(s) + "\n" for s in steps)
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder,
+                        "--dtype", "float32", "--out", out, "--max-tokens", "36"],
+                       input=text, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    refs = [plain_logits(folder, s) for s in seqs.values()]
+    for step, row in ((0, 1), (1, 2)):
+        got = torch.from_numpy(np.fromfile(os.path.join(out, f"{step}.f32"), dtype="<f4")
+                               .reshape(12, V))
+        rows_agree(got, torch.stack([ref[row] for ref in refs]), "float32", f"step {step}")
+    import shutil
+    shutil.rmtree(out, ignore_errors=True)
