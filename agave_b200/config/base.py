@@ -81,8 +81,8 @@ class AttentionSpec:
     position: Optional[RotarySpec] = None
     # the size of a value head where it differs from head_dim (0: the same)
     value_dim: int = 0
-    # a learned logit per query head that joins the softmax denominator once, with no key
-    # and no value and without the scale
+    # a learned logit per query head whose exponential is one more term of the softmax
+    # denominator (unscaled; nothing enters the weighted sum for it)
     sink: bool = False
     q_temp: Optional[QueryTemperatureSpec] = None
     # False: the layer has no key / value projections and attends to what the call that

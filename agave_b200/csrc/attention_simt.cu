@@ -12,8 +12,8 @@
 // src/backend/kernels/cuda/sdpa.zig:14,99).
 //
 // Two options beyond that: a value head size hdv that differs from the query / key head
-// size hd, and a sink per query head: a learned logit with no key and no value that
-// adds exp(sink) to the softmax denominator once (it is not scaled).
+// size hd, and a sink per query head: a learned logit whose exponential is one more term of
+// the softmax denominator (unscaled; nothing is added to the weighted sum for it).
 #include "common.cuh"
 
 constexpr int AT_WARPS = 4;

@@ -3,9 +3,9 @@
 //
 // Router (32-bit): z = W_r x, s = sigmoid(z), choice score c = s + correction.  The experts
 // lie in n_groups equal groups of neighbours; a group's score is the sum of its two largest
-// c; only the experts of the `keep` best groups can be chosen (the others count as minus
-// infinity); the `top` largest c among them win, and their weights are their s, as they
-// are.  n_groups = keep = 1 is plain top-k routing; correction null adds nothing.  Ties go
+// c; the choice is made among the experts of the `keep` best groups alone (every other
+// expert is masked out before the top-k, whatever the sign of the scores); the `top`
+// largest c among them win, and their weights are their s, unchanged.  n_groups = keep = 1 is plain top-k routing; correction null adds nothing.  Ties go
 // to the lower index.
 //
 // Plan: the P = T * top pairs are laid out by expert, every expert's run padded to a

@@ -152,7 +152,7 @@ def test_plain_router_groups_and_negative_scores():
     # six experts in three groups; logits 0 everywhere, so s = 0.5 and the correction
     # decides.  Group sums of choice scores: (-0.5 + -0.6), (-0.1 + -3), (-0.7 + -0.8):
     # groups 0 and 2 stay although group 1 holds the single best expert.  Every choice
-    # score is negative: a dropped group must count as minus infinity, not as 0.
+    # score is negative, so an expert masked to 0 instead of being excluded would win.
     corr = torch.tensor([-1.0, -1.1, -0.6, -3.5, -1.2, -1.3], dtype=torch.float64)
     x = torch.zeros(1, 4, dtype=torch.float64)
     wr = torch.zeros(6, 4, dtype=torch.float64)
