@@ -5,8 +5,8 @@
 // lie in n_groups equal groups of neighbours; a group's score is the sum of its two largest
 // c; the choice is made among the experts of the `keep` best groups alone (every other
 // expert is masked out before the top-k, whatever the sign of the scores); the `top`
-// largest c among them win, and their weights are their s, unchanged.  n_groups = keep = 1 is plain top-k routing; correction null adds nothing.  Ties go
-// to the lower index.
+// largest c among them win, and their weights are their s, unchanged.  n_groups = keep = 1
+// is plain top-k routing; correction null adds nothing.  Ties go to the lower index.
 //
 // Plan: the P = T * top pairs are laid out by expert, every expert's run padded to a
 // multiple of the row tile, so that a tile of the grouped products belongs to one expert.
