@@ -90,7 +90,7 @@ class SimpleTokenizer:
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(
         prog="agave_b200", add_help=False,
-        description="Gemma 3 generation on one B200 (after the agave command line).")
+        description="Generation on one B200 (after the agave command line); the model class follows config.json.")
     p.add_argument("model", nargs="?", help="model folder (config.json + safetensors)")
     p.add_argument("prompt", nargs="?", help="text prompt (needs tokenizer.json)")
     g = p.add_argument_group("GENERAL")

@@ -737,3 +737,44 @@ def test_trace_replay_counts_tokens_not_pages():
         rows_agree(got, torch.stack([ref[row] for ref in refs]), "float32", f"step {step}")
     import shutil
     shutil.rmtree(out, ignore_errors=True)
+
+
+def test_command_line_on_this_architecture():
+    """``python -m agave_b200`` picks the model class from config.json: greedy tokens equal the
+    plain model's, --model-info names the architecture, --profile lists the routed
+    feed-forward's operations, --random-weights draws a model from config.json alone."""
+    name = "R3"
+    folder = folder_for(name, torch.float32)
+    V = vocab(name)
+    prompt = tokens(9, V, 31)
+
+    def run(*args):
+        env = dict(os.environ)
+        env["PYTHONPATH"] = ROOT + os.pathsep + env.get("PYTHONPATH", "")
+        return subprocess.run([sys.executable, "-m", "agave_b200", *args], capture_output=True,
+                              text=True, timeout=900, env=env, cwd=ROOT)
+    toks = ",".join(str(t) for t in prompt)
+    r = run(folder, "--tokens", toks, "-n", "6", "--json", "--dtype", "float32")
+    assert r.returncode == 0, r.stderr[-2000:]
+    out = json.loads(r.stdout.strip().splitlines()[-1])["output_ids"]
+    assert len(out) == 6
+    ref = plain_logits(folder, prompt + out)
+    for k, t in enumerate(out):
+        row = ref[len(prompt) - 1 + k]
+        assert float(row.max() - row[t]) <= 2e-3 * float(row.abs().max()), (k, t)
+    r = run(folder, "--model-info", "--json")
+    assert r.returncode == 0 and "Ramilorn" in r.stdout, r.stderr[-2000:]
+    r = run(folder, "--tokens", toks, "-n", "3", "--profile", "--dtype", "bfloat16")
+    assert r.returncode == 0, r.stderr[-2000:]
+    for op in ("norm", "qkv", "attention", "out_proj", "router", "experts_gate_up", "experts_down",
+               "lm_head", "soft_cap", "TOTAL"):
+        assert op in r.stderr, (op, r.stderr[-1500:])
+    with tempfile.TemporaryDirectory() as d:
+        with open(os.path.join(d, "config.json"), "w") as f:
+            json.dump(CONFIGS[name], f)
+        outs = []
+        for seed in ("3", "3", "4"):
+            r = run(d, "--random-weights", seed, "--tokens", toks, "-n", "5", "--json")
+            assert r.returncode == 0, r.stderr[-2000:]
+            outs.append(json.loads(r.stdout.strip().splitlines()[-1])["output_ids"])
+        assert outs[0] == outs[1] and len(outs[0]) == 5
