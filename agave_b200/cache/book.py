@@ -111,6 +111,7 @@ class GroupGeometry:
     n_pages: int
     entries: List[int] = field(default_factory=list)     # cache entry ids, in order
     value_dim: int = 0                                   # 0: values as wide as keys
+    values_in_keys: bool = False                         # no value pool: values lead the key rows
 
     @property
     def v_dim(self) -> int:
@@ -217,13 +218,14 @@ def plan_groups(requests: Sequence[object], max_tokens: int, max_seq_len: int,
         value_dim = getattr(r, "value_dim", 0)
         if value_dim == r.head_dim:
             value_dim = 0
-        key = (r.n_kv_heads, r.head_dim, window, value_dim)
+        in_keys = bool(getattr(r, "values_in_keys", False))
+        key = (r.n_kv_heads, r.head_dim, window, value_dim, in_keys)
         if key not in index:
             cap = full_cap if window is None else round_up(window, PAGE)
             n_pages = min(budget_pages, n_slots * (cap // PAGE))
             index[key] = len(groups)
             groups.append(GroupGeometry(r.n_kv_heads, r.head_dim, window, cap, max(1, n_pages),
-                                        value_dim=value_dim))
+                                        value_dim=value_dim, values_in_keys=in_keys))
         g = index[key]
         where[entry] = (g, len(groups[g].entries))
         groups[g].entries.append(entry)

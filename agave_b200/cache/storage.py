@@ -3,7 +3,8 @@
 Layout of one group: keys and values ``[entries, pages, PAGE, n_kv_heads,
 head_dim]`` in the compute dtype (the values ``[..., value_dim]`` where a group's
 value heads have a size of their own), and one page table ``[slots, max_pages]``
-(int32) shared by the group's entries.  Position p of the sequence in slot s is
+(int32) shared by the group's entries; a group whose values are the leading part of its key
+rows (a latent that serves as both) has the one pool.  Position p of the sequence in slot s is
 row p % cap; its page is ``page_table[s, row // PAGE]``.  Nothing is cleared
 when a slot is reused: every read is bounded by the sequence's length.
 
@@ -54,7 +55,9 @@ class Cache:
         for g in groups:
             shape = (len(g.entries), g.n_pages, PAGE, g.n_kv_heads)
             self.k_pools.append(torch.zeros(shape + (g.head_dim,), dtype=dtype, device=device))
-            self.v_pools.append(torch.zeros(shape + (g.v_dim,), dtype=dtype, device=device))
+            # (a group whose values lead its key rows has one pool under both names)
+            self.v_pools.append(self.k_pools[-1] if g.values_in_keys else
+                                torch.zeros(shape + (g.v_dim,), dtype=dtype, device=device))
             self.tables.append(torch.zeros((n_slots, g.max_pages), dtype=torch.int32,
                                            device=device))
         # fixed-size state: one tensor per distinct size
@@ -126,6 +129,10 @@ class Cache:
 
     def bytes_held(self) -> int:
         n = 0
+        seen = set()
         for t in self.k_pools + self.v_pools + self.states + self.tables:
+            if t.data_ptr() in seen:
+                continue
+            seen.add(t.data_ptr())
             n += t.numel() * t.element_size()
         return n

@@ -32,9 +32,27 @@ class RotarySpec:
     theta: float = 10000.0
     factor: float = 1.0
     rotary_dim: int = 0          # 0 means the whole head
+    # pairs (2i, 2i + 1) instead of (i, i + rotary_dim/2); a mixer that rotates honours it
+    interleaved: bool = False
+    # frequencies blended between wavelength bounds, and a multiplier on cos and sin
+    scaling: Optional["WavelengthScalingSpec"] = None
 
     def key(self) -> Tuple:
-        return (self.kind, float(self.theta), float(self.factor), int(self.rotary_dim))
+        return (self.kind, float(self.theta), float(self.factor), int(self.rotary_dim),
+                self.scaling)
+
+
+@dataclass(frozen=True)
+class WavelengthScalingSpec:
+    """Frequency scaling by wavelength (the YaRN form).  With pair(t) = dims * ln(original /
+    (2 pi t)) / (2 ln theta), lo = max(floor(pair(fast)), 0), hi = min(ceil(pair(slow)),
+    dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns with
+    f_i / factor * ramp_i + f_i * (1 - ramp_i); cos and sin are multiplied by
+    0.1 ln(factor) + 1."""
+    factor: float = 1.0
+    original: float = 0.0
+    fast: float = 32.0
+    slow: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -53,6 +71,21 @@ class LayerNormSpec:
     kind: str = "layernorm"
     eps: float = 1e-5
     bias: bool = True
+
+
+@dataclass(frozen=True)
+class IdentityNormSpec:
+    """No norm at all: a branch reads the stream itself (rounded to the compute dtype)."""
+    kind: str = "identity"
+
+
+@dataclass(frozen=True)
+class DistanceBiasSpec:
+    """A learned table [rows, heads] added to the scaled score by distance n = t - j >= 0:
+    row n for n < rows/2, else min(rows - 1, rows/2 + floor(ln(n / (rows/2)) / ln(far /
+    (rows/2)) * (rows - rows/2)))."""
+    rows: int = 0
+    far: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -88,10 +121,39 @@ class AttentionSpec:
     # False: the layer has no key / value projections and attends to what the call that
     # writes its cache entry stored (the run order names that entry)
     own_kv: bool = True
+    # q and k are RMS-normed over their whole projection (all heads at once, a weight of
+    # that width) instead of head by head; eps and centring come from ``qk_norm``
+    qk_norm_whole: bool = False
+    # a sink whose logit is this constant instead of a learned tensor (0.0: one is added to
+    # the softmax denominator)
+    fixed_sink: Optional[float] = None
+    distance_bias: Optional[DistanceBiasSpec] = None
 
     @property
     def v_dim(self) -> int:
         return self.value_dim or self.head_dim
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal softmax attention whose keys and values are rebuilt from a cached latent.
+
+    Per position the cache holds c = rmsnorm(W_dkv x)[:kv_rank] and one rotated key part kr
+    (rot_dim wide) that all heads share.  Head a scores (q_a[:head_dim] . (W_uk c)_a +
+    rot(q_a[head_dim:]) . kr) * scale and weighs (W_uv c)_a.  ``q_rank`` > 0: the queries
+    come through a normed latent of that size too.  ``gate``: the heads' outputs are
+    multiplied by sigmoid(W_g x), "element" by element or one value per "head"."""
+    kind: str = "latent_attention"
+    n_heads: int = 0
+    head_dim: int = 0            # unrotated part of a query / key head
+    rot_dim: int = 0             # rotated part
+    value_dim: int = 0
+    kv_rank: int = 0
+    q_rank: int = 0
+    scale: float = 1.0
+    eps: float = 1e-6
+    position: Optional[RotarySpec] = None
+    gate: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -100,6 +162,14 @@ class GatedFeedForwardSpec:
     kind: str = "gated_dense"
     intermediate_size: int = 0
     activation: str = "gelu_tanh"
+
+
+@dataclass(frozen=True)
+class DenseFeedForwardSpec:
+    """down(act(up x)), dense, no gate; "relu2" is max(z, 0)^2."""
+    kind: str = "dense"
+    intermediate_size: int = 0
+    activation: str = "relu2"
 
 
 @dataclass(frozen=True)
@@ -125,7 +195,9 @@ class BlockSpec:
 
     arrangement "sandwich": h += post(mixer(pre(h))); h += post(ffn(pre(h)))
     (src/models/gemma3.zig:708-709,824-826,835-836,876-878);
-    arrangement "pre": the same without the two post norms.
+    arrangement "pre": the same without the two post norms;
+    arrangement "post": the same without the two pre norms (the branches read the stream
+    itself).
     ``kind`` names the block class in the block registry; "sequential" is the
     class that runs the mixer and then the feed-forward, as above.  Another
     arrangement of parts (both branches from one norm, no feed-forward at all)

@@ -14,6 +14,8 @@
 // Two options beyond that: a value head size hdv that differs from the query / key head
 // size hd, and a sink per query head: a learned logit whose exponential is one more term of
 // the softmax denominator (unscaled; nothing is added to the weighted sum for it).
+// A bias per (distance, head) may be added to the scaled score, and the cache's value rows
+// may lie at a stride of their own (values that are the leading part of the key rows).
 #include "common.cuh"
 
 constexpr int AT_WARPS = 4;
@@ -25,6 +27,13 @@ struct PagedKV {
     const int* page_table;     // [n_slots, max_pages]
     const int* slots;          // [B]
     int max_pages, page, cap;
+    int v_row;                 // elements between two positions' value rows (0: nkv * hdv)
+};
+
+// A learned bias per (distance, head) added to the scaled score: bias[min(p - j, n - 1), h].
+struct DistanceBias {
+    const float* bias;         // [n, nh] or null
+    int n;
 };
 
 template <typename T, bool PAGED>
@@ -34,7 +43,7 @@ attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T* __re
                       const int* __restrict__ positions, const int* __restrict__ seq_index,
                       const int* __restrict__ cu_seqlens, PagedKV pk, int n_tokens, int nh, int nkv,
                       int hd, float scale, int window, int hdv, long long v_stride,
-                      const float* __restrict__ sinks) {
+                      const float* __restrict__ sinks, DistanceBias db) {
     pdl_wait();
     pdl_launch_next();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -69,9 +78,9 @@ attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T* __re
         if (PAGED) {
             const int row = j % pk.cap;
             const int page = pk.page_table[(size_t)slot * pk.max_pages + row / pk.page];
-            const size_t off = ((size_t)page * pk.page + row % pk.page) * nkv + g;
-            kp = (const T*)pk.k_pool + off * hd;
-            vp = (const T*)pk.v_pool + off * hdv;
+            const size_t at = (size_t)page * pk.page + row % pk.page;
+            kp = (const T*)pk.k_pool + (at * nkv + g) * hd;
+            vp = (const T*)pk.v_pool + at * pk.v_row + (size_t)g * hdv;
         } else {
             kp = k + (base + j) * kv_stride + (size_t)g * hd;
             vp = v + (base + j) * v_stride + (size_t)g * hdv;
@@ -83,6 +92,7 @@ attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T* __re
             if (e < hd) s = fmaf(qr[i], to_f32(kp[e]), s);
         }
         s = warp_sum(s) * scale;
+        if (db.bias) s += db.bias[(size_t)min(p - j, db.n - 1) * nh + h];
         const float mn = fmaxf(m, s);
         const float alpha = expf(m - mn);      // exp(-inf) = 0 on the first key
         const float w = expf(s - mn);
@@ -134,20 +144,23 @@ AGV_API int agv_attention_prefill_simt_ex(const void* q, long long q_stride, con
                                           const int* cu_seqlens, int n_tokens, int nh, int nkv,
                                           int hd, float scale, int window, int hdv,
                                           long long v_stride, const float* sinks,
+                                          const float* dist_bias, int n_dist,
                                           cudaStream_t stream) {
     if (int rc = check_attn(n_tokens, nh, nkv, hd, window, hdv)) return rc;
+    AGV_REQUIRE(!dist_bias || n_dist > 0, "attention: an empty distance table");
     if (n_tokens == 0) return 0;
+    DistanceBias db{dist_bias, n_dist};
     const long long items = (long long)n_tokens * nh;
     const unsigned grid = (unsigned)((items + AT_WARPS - 1) / AT_WARPS);
     PagedKV pk{};
     if (dtype == AGV_F32)
         agv_launch(attention_simt_kernel<float, false>, grid, AT_WARPS * 32, 0, stream, (const float*)q, q_stride, (const float*)k, (const float*)v, kv_stride, (float*)out,
             positions, seq_index, cu_seqlens, pk, n_tokens, nh, nkv, hd, scale, window, hdv,
-            v_stride, sinks);
+            v_stride, sinks, db);
     else if (dtype == AGV_BF16)
         agv_launch(attention_simt_kernel<__nv_bfloat16, false>, grid, AT_WARPS * 32, 0, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
             kv_stride, (__nv_bfloat16*)out, positions, seq_index, cu_seqlens, pk, n_tokens, nh,
-            nkv, hd, scale, window, hdv, v_stride, sinks);
+            nkv, hd, scale, window, hdv, v_stride, sinks, db);
     else
         return agv_fail(-1, "attention: unknown dtype %d", dtype);
     AGV_LAUNCH_OK("attention_simt_kernel");
@@ -161,7 +174,7 @@ AGV_API int agv_attention_prefill_simt(const void* q, long long q_stride, const 
                                        float scale, int window, cudaStream_t stream) {
     return agv_attention_prefill_simt_ex(q, q_stride, k, v, kv_stride, out, dtype, positions,
                                          seq_index, cu_seqlens, n_tokens, nh, nkv, hd, scale,
-                                         window, hd, kv_stride, nullptr, stream);
+                                         window, hd, kv_stride, nullptr, nullptr, 0, stream);
 }
 
 // Queries against the paged cache (the query's own key is already stored).
@@ -174,21 +187,25 @@ AGV_API int agv_attention_paged_simt_ex(const void* q, long long q_stride, void*
                                         const int* positions, const int* seq_index, int max_pages,
                                         int page, int cap, int n_tokens, int nh, int nkv, int hd,
                                         float scale, int window, int hdv, const float* sinks,
+                                        const float* dist_bias, int n_dist, int v_row,
                                         cudaStream_t stream) {
     if (int rc = check_attn(n_tokens, nh, nkv, hd, window, hdv)) return rc;
+    AGV_REQUIRE(!dist_bias || n_dist > 0, "attention: an empty distance table");
+    AGV_REQUIRE(v_row == 0 || v_row >= nkv * hdv, "attention: value rows overlap");
+    DistanceBias db{dist_bias, n_dist};
     AGV_REQUIRE(page > 0 && cap > 0 && max_pages > 0, "attention: bad cache geometry");
     AGV_REQUIRE(window == 0 || window <= cap, "attention: window %d exceeds the ring of %d rows",
                 window, cap);
     if (n_tokens == 0) return 0;
     const long long items = (long long)n_tokens * nh;
     const unsigned grid = (unsigned)((items + AT_WARPS - 1) / AT_WARPS);
-    PagedKV pk{k_pool, v_pool, page_table, slots, max_pages, page, cap};
+    PagedKV pk{k_pool, v_pool, page_table, slots, max_pages, page, cap, v_row ? v_row : nkv * hdv};
     if (dtype == AGV_F32)
         agv_launch(attention_simt_kernel<float, true>, grid, AT_WARPS * 32, 0, stream, (const float*)q, q_stride, nullptr, nullptr, 0, (float*)out, positions, seq_index,
-            nullptr, pk, n_tokens, nh, nkv, hd, scale, window, hdv, 0LL, sinks);
+            nullptr, pk, n_tokens, nh, nkv, hd, scale, window, hdv, 0LL, sinks, db);
     else if (dtype == AGV_BF16)
         agv_launch(attention_simt_kernel<__nv_bfloat16, true>, grid, AT_WARPS * 32, 0, stream, (const __nv_bfloat16*)q, q_stride, nullptr, nullptr, 0, (__nv_bfloat16*)out, positions,
-            seq_index, nullptr, pk, n_tokens, nh, nkv, hd, scale, window, hdv, 0LL, sinks);
+            seq_index, nullptr, pk, n_tokens, nh, nkv, hd, scale, window, hdv, 0LL, sinks, db);
     else
         return agv_fail(-1, "attention: unknown dtype %d", dtype);
     AGV_LAUNCH_OK("attention_simt_kernel");
@@ -203,5 +220,5 @@ AGV_API int agv_attention_paged_simt(const void* q, long long q_stride, void* ou
                                      cudaStream_t stream) {
     return agv_attention_paged_simt_ex(q, q_stride, out, dtype, k_pool, v_pool, page_table, slots,
                                        positions, seq_index, max_pages, page, cap, n_tokens, nh,
-                                       nkv, hd, scale, window, hd, nullptr, stream);
+                                       nkv, hd, scale, window, hd, nullptr, nullptr, 0, 0, stream);
 }

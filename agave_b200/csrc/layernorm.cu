@@ -2,7 +2,7 @@
 // the same fusion the RMS norm family has: the norm of a branch's output, the residual
 // sum (times a constant multiplier) and the norm that feeds the next branch in one launch.
 //
-//   y == null:  x = N(h[rows]; w_next, b_next)
+//   y == null:  x = N(h[rows]; w_next, b_next)       (x = h[rows] without w_next)
 //   else:       b = sum_s y[s];  b = N(b; w_post, b_post) if w_post;  b *= mult;
 //               h += b if add_residual;  v = h (or b);
 //               x = N(v; w_next, b_next) if w_next, else x = v if x is given.
@@ -300,8 +300,7 @@ AGV_API int agv_layer_norm_join(float* h, const void* y, int y_dtype, int n_spli
     AGV_REQUIRE(R >= 0 && H > 0, "layer_norm: bad sizes R=%d H=%d", R, H);
     AGV_REQUIRE(H <= 16 * 1024, "layer_norm: rows of %d values exceed the %d this kernel keeps in "
                 "registers", H, 16 * 1024);
-    AGV_REQUIRE(y || (w_next && x && h), "layer_norm: without a branch input, h, w_next and x are "
-                "needed");
+    AGV_REQUIRE(y || (x && h), "layer_norm: without a branch input, h and x are needed");
     AGV_REQUIRE(!y || n_splits >= 1, "layer_norm: n_splits must be >= 1");
     AGV_REQUIRE(!(y && rows), "layer_norm: row gather is only for the plain norm");
     AGV_REQUIRE(!add_residual || h, "layer_norm: the residual sum needs h");

@@ -150,6 +150,20 @@ def rope_table(positions: torch.Tensor, rotary_dim: int, theta: float, factor: f
                                         ctypes.c_double(theta), ctypes.c_double(factor), _stream()))
 
 
+def rope_table_freqs(positions: torch.Tensor, freqs: torch.Tensor, mult: float,
+                     cos: torch.Tensor, sin: torch.Tensor) -> None:
+    """cos, sin [T, n] = mult * cos / sin(p * freqs[i]); freqs [n] 64-bit on the device."""
+    _i32(positions, "positions"); _f32(cos, "cos"); _f32(sin, "sin")
+    if freqs.dtype != torch.float64:
+        raise KernelError("freqs must be float64")
+    T, half = positions.numel(), freqs.numel()
+    assert cos.shape == (T, half) and sin.shape == cos.shape
+    _dense(cos, "cos"); _dense(sin, "sin"); _dense(freqs, "freqs")
+    with _span("rope_table", _nbytes(cos, sin)):
+        _check(library().agv_rope_table_freqs(_ptr(positions), _ptr(freqs), _ptr(cos), _ptr(sin),
+                                              T, half, ctypes.c_double(mult), _stream()))
+
+
 # ---------------------------------------------------------------------- norms
 def norm_residual(h: Optional[torch.Tensor], y: Optional[torch.Tensor],
                   w_post: Optional[torch.Tensor], w_next: Optional[torch.Tensor],
@@ -527,20 +541,26 @@ def attention_prefill_simt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ou
                            positions: torch.Tensor, seq_index: torch.Tensor,
                            cu_seqlens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                            scale: float, window: int, value_dim: int = 0,
-                           sinks: Optional[torch.Tensor] = None) -> None:
+                           sinks: Optional[torch.Tensor] = None,
+                           dist_bias: Optional[torch.Tensor] = None) -> None:
     """Prompts that start at 0; q [T, nh*hd], k [T, nkv*hd], v [T, nkv*hdv] row-strided
     views (hdv = value_dim or head_dim), out [T, nh*hdv]; ``sinks`` [nh]: a logit per query
-    head that joins its softmax denominator once."""
+    head that joins its softmax denominator once; ``dist_bias`` [n, nh]: added to the scaled
+    score of a key at distance min(t - j, n - 1)."""
     T = q.shape[0]
     assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1
-    _dense(out, "out"); _f32(sinks, "sinks")
+    _dense(out, "out"); _f32(sinks, "sinks"); _f32(dist_bias, "dist_bias")
+    if dist_bias is not None:
+        _dense(dist_bias, "dist_bias")
+        assert dist_bias.dim() == 2 and dist_bias.shape[1] == n_heads
     _i32(positions, "positions"); _i32(seq_index, "seq_index"); _i32(cu_seqlens, "cu_seqlens")
     _check(library().agv_attention_prefill_simt_ex(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), _ptr(v),
         ctypes.c_longlong(k.stride(0)), _ptr(out), dtype_code(q.dtype), _ptr(positions),
         _ptr(seq_index), _ptr(cu_seqlens), T, n_heads, n_kv_heads, head_dim,
         ctypes.c_float(scale), window, value_dim or head_dim, ctypes.c_longlong(v.stride(0)),
-        _ptr(sinks), _stream()))
+        _ptr(sinks), _ptr(dist_bias), dist_bias.shape[0] if dist_bias is not None else 0,
+        _stream()))
 
 
 def attention_paged_simt(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor,
@@ -548,11 +568,17 @@ def attention_paged_simt(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tenso
                          positions: torch.Tensor, seq_index: torch.Tensor, page: int, cap: int,
                          n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                          window: int, value_dim: int = 0,
-                         sinks: Optional[torch.Tensor] = None) -> None:
-    """Queries against the paged cache; their own keys are already stored."""
+                         sinks: Optional[torch.Tensor] = None,
+                         dist_bias: Optional[torch.Tensor] = None, v_row: int = 0) -> None:
+    """Queries against the paged cache; their own keys are already stored.  ``v_row``: the
+    elements between two positions' value rows where that is not nkv * hdv (values that are
+    the leading part of the key rows: v_pool is then k_pool)."""
     T = q.shape[0]
     assert q.stride(1) == 1
-    _f32(sinks, "sinks")
+    _f32(sinks, "sinks"); _f32(dist_bias, "dist_bias")
+    if dist_bias is not None:
+        _dense(dist_bias, "dist_bias")
+        assert dist_bias.dim() == 2 and dist_bias.shape[1] == n_heads
     _dense(out, "out"); _dense(k_pool, "k_pool"); _dense(v_pool, "v_pool")
     for t, n in ((positions, "positions"), (page_table, "page_table"), (slots, "slots"),
                  (seq_index, "seq_index")):
@@ -562,7 +588,147 @@ def attention_paged_simt(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tenso
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(out), dtype_code(q.dtype), _ptr(k_pool),
         _ptr(v_pool), _ptr(page_table), _ptr(slots), _ptr(positions), _ptr(seq_index),
         page_table.shape[1], page, cap, T, n_heads, n_kv_heads, head_dim,
-        ctypes.c_float(scale), window, value_dim or head_dim, _ptr(sinks), _stream()))
+        ctypes.c_float(scale), window, value_dim or head_dim, _ptr(sinks), _ptr(dist_bias),
+        dist_bias.shape[0] if dist_bias is not None else 0, int(v_row), _stream()))
+
+
+# ------------------------------------------- rows of stacked projections, latent attention
+def _cache_args(view, ctx):
+    if view is None:
+        return [ctypes.c_void_p(0)] * 6 + [0, 0, 0]
+    return [_ptr(view.k_pool), _ptr(view.v_pool), _ptr(view.page_table), _ptr(ctx.slots),
+            _ptr(ctx.lens), _ptr(ctx.seq_index), view.page_table.shape[1], view.page, view.cap]
+
+
+def _row_input(row, partial, T, W):
+    """(row pointer, row stride, partial pointer, n_splits) of a stacked projection's output:
+    [T, W] in the compute dtype, or [S, T, W] 32-bit partial sums."""
+    if partial is not None:
+        _f32(partial, "partial"); _dense(partial, "partial")
+        assert partial.dim() == 3 and partial.shape[1:] == (T, W)
+        return ctypes.c_void_p(0), 0, _ptr(partial), partial.shape[0]
+    assert row.shape == (T, W) and row.stride(1) == 1
+    return _ptr(row), row.stride(0), ctypes.c_void_p(0), 0
+
+
+def proj_norm_store(out: torch.Tensor, nq: int, nk: int, nv: int, wq: torch.Tensor,
+                    wk: torch.Tensor, eps: float, positions: torch.Tensor, view=None, ctx=None,
+                    partial: Optional[torch.Tensor] = None) -> None:
+    """out [T, nq + nk + nv] = q | k | v of a stacked projection with q and k each RMS-normed
+    over their whole width (weights wq [nq], wk [nk], 32-bit); the input is ``partial``
+    ([S, T, W] 32-bit partial sums) or out itself.  With ``view`` (a cache entry's pools) the
+    k and v parts also go to the cache rows of the tokens' positions."""
+    T, W = out.shape
+    assert W == nq + nk + nv and out.stride(1) == 1
+    _f32(wq, "wq"); _f32(wk, "wk"); _i32(positions, "positions")
+    rp, ld, pp, ns = _row_input(out, partial, T, W)
+    cache = _cache_args(view, ctx)
+    if view is not None:
+        assert view.k_pool.dtype == out.dtype
+    with _span("qk_norm_rope", 2 * _nbytes(out) + _nbytes(partial)):
+        _check(library().agv_proj_norm_store(
+            rp, ctypes.c_longlong(ld), pp, ns, _ptr(out), ctypes.c_longlong(out.stride(0)),
+            dtype_code(out.dtype), T, nq, nk, nv, _ptr(wq), _ptr(wk), ctypes.c_float(eps),
+            _ptr(positions), *cache, _stream()))
+
+
+def latent_prepare(out: torch.Tensor, q_width: int, q_latent: bool, heads: int, d: int, r: int,
+                   R: int, G: int, w_q: Optional[torch.Tensor], w_c: torch.Tensor, eps: float,
+                   cos: torch.Tensor, sin: torch.Tensor, interleaved: bool,
+                   positions: torch.Tensor, view=None, ctx=None,
+                   partial: Optional[torch.Tensor] = None) -> None:
+    """out [T, q_width + R + r + G] = Q | c | kr | g of a latent-attention mixer's stacked
+    projection: c RMS-normed (w_c [R]), kr rotated by position, c | kr stored as the cache row
+    (``view``), g passed through, and Q either normed as a latent (``q_latent``, w_q
+    [q_width]) or, as [heads, d + r], with the last r of every head rotated."""
+    T, W = out.shape
+    assert W == q_width + R + r + G and out.stride(1) == 1
+    _f32(w_q, "w_q"); _f32(w_c, "w_c"); _f32(cos, "cos"); _f32(sin, "sin")
+    _i32(positions, "positions"); _dense(cos, "cos"); _dense(sin, "sin")
+    assert cos.shape == (T, r // 2) and sin.shape == cos.shape
+    rp, ld, pp, ns = _row_input(out, partial, T, W)
+    cache = _cache_args(view, ctx)
+    if view is not None:
+        assert view.k_pool.dtype == out.dtype and view.k_pool.shape[-1] * view.k_pool.shape[-2] == R + r
+    del cache[1]                                 # one pool: the latent rows
+    with _span("qk_norm_rope", 2 * _nbytes(out) + _nbytes(partial)):
+        _check(library().agv_latent_prepare(
+            rp, ctypes.c_longlong(ld), pp, ns, _ptr(out), ctypes.c_longlong(out.stride(0)),
+            dtype_code(out.dtype), T, q_width, 1 if q_latent else 0, heads, d, r, R, G,
+            _ptr(w_q), _ptr(w_c), ctypes.c_float(eps), _ptr(cos), _ptr(sin),
+            1 if interleaved else 0, _ptr(positions), *cache, _stream()))
+
+
+def rotate_heads(x: torch.Tensor, heads: int, head_width: int, r: int, cos: torch.Tensor,
+                 sin: torch.Tensor, interleaved: bool) -> None:
+    """x [T, heads * head_width] in place: the last r of every head rotated by the tables."""
+    T = x.shape[0]
+    assert x.shape[1] == heads * head_width and x.stride(1) == 1
+    _f32(cos, "cos"); _f32(sin, "sin"); _dense(cos, "cos"); _dense(sin, "sin")
+    assert cos.shape == (T, r // 2)
+    with _span("qk_norm_rope", 2 * T * heads * r * x.element_size()):
+        _check(library().agv_rotate_heads(_ptr(x), ctypes.c_longlong(x.stride(0)),
+                                          dtype_code(x.dtype), T, heads, head_width, r, _ptr(cos),
+                                          _ptr(sin), 1 if interleaved else 0, _stream()))
+
+
+def assemble_keys(k_plain: torch.Tensor, kr: torch.Tensor, k_out: torch.Tensor, heads: int,
+                  d: int, r: int) -> None:
+    """k_out [T, heads * (d + r)]: head a is k_plain[t, a * d:(a + 1) * d] followed by kr[t]."""
+    T = k_out.shape[0]
+    assert k_plain.shape == (T, heads * d) and kr.shape == (T, r) and k_out.shape[1] == heads * (d + r)
+    assert k_plain.stride(1) == 1 and kr.stride(1) == 1 and k_plain.dtype == kr.dtype == k_out.dtype
+    _dense(k_out, "k_out")
+    with _span("qk_norm_rope", 2 * _nbytes(k_out)):
+        _check(library().agv_assemble_keys(_ptr(k_plain), ctypes.c_longlong(k_plain.stride(0)),
+                                           _ptr(kr), ctypes.c_longlong(kr.stride(0)), _ptr(k_out),
+                                           dtype_code(k_out.dtype), T, heads, d, r, _stream()))
+
+
+def heads_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, op: str = "heads_linear") -> None:
+    """out[t, a, :] = w[a] x[t, a, :]: x [T, heads, K] and out [T, heads, N] are views with
+    unit innermost stride, w [heads, N, K] dense; out in x's dtype or 32-bit."""
+    T, A, K = x.shape
+    N = w.shape[1]
+    assert w.shape == (A, N, K) and out.shape == (T, A, N) and x.dtype == w.dtype
+    assert x.stride(2) == 1 and out.stride(2) == 1
+    _dense(w, "w")
+    out_f32 = out.dtype == torch.float32 and x.dtype != torch.float32
+    assert out_f32 or out.dtype == x.dtype
+    with _span(op, _nbytes(w, x, out), 2 * T * A * N * K):
+        _check(library().agv_heads_linear(
+            _ptr(x), ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(x.stride(1)), _ptr(w),
+            _ptr(out), ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out.stride(1)),
+            dtype_code(x.dtype), 1 if out_f32 else 0, T, A, N, K, _stream()))
+
+
+def gate_sigmoid(out: torch.Tensor, g: torch.Tensor) -> None:
+    """out [T, n] *= sigmoid(g [T, m]) in place; each g value covers n / m neighbours."""
+    T, n = out.shape
+    m = g.shape[1]
+    assert g.shape[0] == T and n % m == 0 and out.stride(1) == 1 and g.stride(1) == 1
+    assert out.dtype == g.dtype
+    with _span("gate", 2 * _nbytes(out) + _nbytes(g)):
+        _check(library().agv_gate_sigmoid(_ptr(out), ctypes.c_longlong(out.stride(0)), _ptr(g),
+                                          ctypes.c_longlong(g.stride(0)), dtype_code(out.dtype),
+                                          T, n, n // m, _stream()))
+
+
+def relu2(z: torch.Tensor) -> None:
+    """z <- max(z, 0)^2 in place."""
+    _dense(z, "z")
+    with _span("activation", 2 * _nbytes(z)):
+        _check(library().agv_relu2(_ptr(z), ctypes.c_longlong(z.numel()), dtype_code(z.dtype),
+                                   _stream()))
+
+
+def linear_activated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, activation: str,
+                     op: str = "linear") -> None:
+    """out = act(x w^T); "relu2" is the squared relu."""
+    if activation != "relu2":
+        raise KernelError(f"linear_activated: unknown activation {activation!r}")
+    linear(x, w, out, op=op)
+    relu2(out)
 
 
 # ------------------------------------------------------------------- sampling
@@ -971,14 +1137,14 @@ def attention_prefill_wants_transposed_values(qkv: torch.Tensor, head_dim: int,
 
 
 def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, window,
-                      vt=None, value_dim: int = 0, sinks=None) -> None:
+                      vt=None, value_dim: int = 0, sinks=None, dist_bias=None) -> None:
     """Prompt attention of one layer in bfloat16: the tcgen05 kernel for head sizes
     in steps of 16 up to 256, the mma.sync kernel for the other multiples of 8; else
     (and for value heads of another size than the keys') the one-warp-per-(token, head)
     kernel.  ``sinks`` [nh]: a logit per query head that joins its denominator once."""
     hdv = value_dim or head_dim
     aligned = (q.dtype == torch.bfloat16 and head_dim <= 256 and hdv == head_dim and
-               k.stride(0) == v.stride(0) and
+               dist_bias is None and k.stride(0) == v.stride(0) and
                q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and
                k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0)
     with _span("attention", *_attention_cost(ctx, q, k, v, out, n_heads, head_dim, window)):
@@ -992,7 +1158,7 @@ def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, w
         else:
             attention_prefill_simt(q, k, v, out, ctx.positions, ctx.seq_index, ctx.cu_seqlens,
                                    n_heads, n_kv_heads, head_dim, scale, window, value_dim=hdv,
-                                   sinks=sinks)
+                                   sinks=sinks, dist_bias=dist_bias)
 
 
 def _attention_cost(ctx, q, k, v, out, n_heads, head_dim, window, n_kv_heads=0):
@@ -1151,14 +1317,16 @@ def attention_decode_fused(partial: torch.Tensor, wq: Optional[torch.Tensor],
 
 
 def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, window,
-                     value_dim: int = 0, sinks=None) -> None:
+                     value_dim: int = 0, sinks=None, dist_bias=None,
+                     values_in_keys: bool = False) -> None:
     """Decode attention of one layer: the split kernel for head sizes in steps of
     16 up to 512, else (and for value heads of another size than the keys') the
     one-warp-per-head kernel."""
     hdv = value_dim or head_dim
     with _span("attention", *_attention_cost(ctx, q, None, None, out, n_heads, head_dim, window,
                                              n_kv_heads)):
-        if head_dim % 16 == 0 and head_dim <= 512 and hdv == head_dim:
+        if (head_dim % 16 == 0 and head_dim <= 512 and hdv == head_dim and dist_bias is None
+                and not values_in_keys):
             max_keys = min(window, ctx.max_len) if window else ctx.max_len
             attention_decode_split(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
                                    ctx.positions, view.page, view.cap, n_heads, n_kv_heads,
@@ -1166,4 +1334,6 @@ def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, wi
         else:
             attention_paged_simt(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
                                  ctx.positions, ctx.seq_index, view.page, view.cap, n_heads,
-                                 n_kv_heads, head_dim, scale, window, value_dim=hdv, sinks=sinks)
+                                 n_kv_heads, head_dim, scale, window, value_dim=hdv, sinks=sinks,
+                                 dist_bias=dist_bias,
+                                 v_row=n_kv_heads * head_dim if values_in_keys else 0)

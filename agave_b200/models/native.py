@@ -80,7 +80,10 @@ def standard_blocks(model) -> bool:
         for n in (b.pre_mixer_norm, b.pre_ffn_norm, b.post_mixer_norm, b.post_ffn_norm):
             if n is not None and type(n) is not RMSNorm:
                 return False
-        if b.mixer.position is not None and type(b.mixer.position) is not RotaryEmbedding:
+        if b.mixer.position is not None and (
+                type(b.mixer.position) is not RotaryEmbedding or
+                getattr(b.mixer.position, "scaling", None) is not None or
+                getattr(b.mixer.position, "interleaved", False)):
             return False
         # options the C++ step function does not describe: a sink, a query temperature,
         # value heads of their own size, a multiplier on the branches

@@ -2,10 +2,11 @@ from .base import (KVRequest, ParamSpec, StateRequest, block_class, feed_forward
                    mixer_class, norm_class, position_class, register_block,
                    register_feed_forward, register_mixer, register_norm, register_position,
                    register_stream_position, stream_position_class)
-from .norm import LayerNorm, RMSNorm
+from .norm import Identity, LayerNorm, RMSNorm
 from .rope import RotaryEmbedding
 from .attention import AttentionMixer
-from .feedforward import GatedFeedForward
+from .latent import LatentAttentionMixer
+from .feedforward import DenseFeedForward, GatedFeedForward
 from .moe import RoutedFeedForward
 from .block import Block
 from .linear import GatedLinear, Linear
@@ -14,5 +15,6 @@ __all__ = ["KVRequest", "ParamSpec", "StateRequest", "feed_forward_class", "mixe
            "norm_class", "position_class", "block_class", "stream_position_class",
            "register_block", "register_feed_forward", "register_mixer", "register_norm",
            "register_position", "register_stream_position", "RMSNorm", "LayerNorm",
-           "RoutedFeedForward", "RotaryEmbedding",
+           "RoutedFeedForward", "RotaryEmbedding", "Identity", "LatentAttentionMixer",
+           "DenseFeedForward",
            "AttentionMixer", "GatedFeedForward", "Block", "GatedLinear", "Linear"]

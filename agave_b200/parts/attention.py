@@ -25,10 +25,15 @@ than the keys' (``value_dim``), a sink logit per query head that joins the softm
 denominator once (``sink``; tensor ``sink``), a query temperature that multiplies q by
 1 + coef * ln(floor((p + 1) / every) + 1) at position p (``q_temp``), and no key / value
 projections at all (``own_kv`` False: the layer attends with its own queries to the keys
-and values of the cache entry the run order names).
+and values of the cache entry the run order names); q and k normed over the whole
+projection instead of head by head (``qk_norm_whole``), a sink of constant logit
+(``fixed_sink``), and a learned bias by distance added to the scaled scores
+(``distance_bias``; tensor ``distance_bias`` [rows, heads], expanded at load time into one
+row per distance).
 """
 from __future__ import annotations
 
+import math
 from typing import Dict, Optional
 
 import torch
@@ -58,9 +63,23 @@ class AttentionMixer:
         self.q_temp = (float(qt.coef), int(qt.every)) if qt is not None and qt.coef != 0 else None
         if self.q_temp is not None and self.q_temp[1] < 1:
             raise ValueError("the query temperature's period must be at least 1")
+        self.whole_norm = bool(getattr(spec, "qk_norm_whole", False))
+        self.dist_spec = getattr(spec, "distance_bias", None)
+        self.dist_bias: Optional[torch.Tensor] = None
+        fixed = getattr(spec, "fixed_sink", None)
+        self.fixed_sink = None if fixed is None else float(fixed)
+        if self.whole_norm and (spec.qk_norm is None or self.position is not None or
+                                self.q_temp is not None or not self.own_kv):
+            raise ValueError("a norm over the whole projection needs qk_norm and goes without a "
+                             "rotation, a query temperature or borrowed keys and values")
+        if self.fixed_sink is not None and getattr(spec, "sink", False):
+            raise ValueError("a sink is either learned or a constant, not both")
+        if self.position is not None and getattr(self.position, "interleaved", False):
+            raise ValueError("this mixer rotates split halves only")
         # the options the standard kernels' callers do not pass
         self.plain = (self.own_kv and self.value_dim == spec.head_dim and self.q_temp is None
-                      and not getattr(spec, "sink", False))
+                      and not getattr(spec, "sink", False) and not self.whole_norm
+                      and self.dist_spec is None and self.fixed_sink is None)
 
     @classmethod
     def param_specs(cls, spec: AttentionSpec, hidden_size: int) -> Dict[str, ParamSpec]:
@@ -74,12 +93,32 @@ class AttentionMixer:
         p["o_proj.weight"] = ParamSpec((hidden_size, spec.n_heads * vd))
         if spec.qk_norm is not None:
             zc = spec.qk_norm.zero_centered
-            p["q_norm.weight"] = ParamSpec((spec.head_dim,), "norm", zero_centered=zc)
+            whole = getattr(spec, "qk_norm_whole", False)
+            p["q_norm.weight"] = ParamSpec((q if whole else spec.head_dim,), "norm",
+                                           zero_centered=zc)
             if own_kv:
-                p["k_norm.weight"] = ParamSpec((spec.head_dim,), "norm", zero_centered=zc)
+                p["k_norm.weight"] = ParamSpec((kv if whole else spec.head_dim,), "norm",
+                                               zero_centered=zc)
         if getattr(spec, "sink", False):
             p["sink"] = ParamSpec((spec.n_heads,), "float32")
+        db = getattr(spec, "distance_bias", None)
+        if db is not None:
+            p["distance_bias"] = ParamSpec((db.rows, spec.n_heads), "float32")
         return p
+
+    @staticmethod
+    def distance_rows(rows: int, far: float, n: int):
+        """The table row of each distance 0..n-1: a row each for the first rows/2 distances,
+        then rows that grow logarithmically and end at ``far``."""
+        half = rows // 2
+        out = []
+        for dist in range(n):
+            if dist < half:
+                out.append(dist)
+            else:
+                out.append(min(rows - 1, half + int(math.floor(
+                    math.log(dist / half) / math.log(far / half) * (rows - half)))))
+        return out
 
     def cache_request(self):
         if not self.own_kv:
@@ -109,6 +148,19 @@ class AttentionMixer:
                                       + add).contiguous()
         if getattr(self.spec, "sink", False):
             self.sinks = tensors["sink"].to(device=device, dtype=torch.float32).contiguous()
+        if self.fixed_sink is not None:
+            self.sinks = torch.full((self.spec.n_heads,), self.fixed_sink, dtype=torch.float32,
+                                    device=device)
+        if self.dist_spec is not None:
+            # one row per distance a query can see; the last row stands for all farther ones
+            # (from ``far`` on every distance has the table's last row)
+            db = self.dist_spec
+            n = int(math.ceil(db.far)) + 1
+            if self.spec.window:
+                n = min(n, int(self.spec.window))
+            idx = torch.tensor(self.distance_rows(db.rows, db.far, max(n, 1)), device=device)
+            table = tensors["distance_bias"].to(device=device, dtype=torch.float32)
+            self.dist_bias = table[idx].contiguous()
 
     def forward(self, x: torch.Tensor, ctx, cache_entry: int, writes_cache: bool) -> torch.Tensor:
         if not self.plain:
@@ -196,7 +248,8 @@ class AttentionMixer:
         width = (nh + n_own) * hd + n_own * hdv
         proj = self.qkv.partial(x, cheap_sum=True)
         part = proj if proj.dim() == 3 else None
-        if (ctx.mode == DECODE and part is not None and hdv == hd and
+        if (ctx.mode == DECODE and part is not None and hdv == hd and not self.whole_norm and
+                self.dist_bias is None and
                 kernels.attention_decode_fused_supported(self.dtype, hd, rotary_dim)):
             out = ctx.new(T, nh * hdv)
             kernels.attention_decode_fused(part, self.q_norm_weight, self.k_norm_weight, eps, cos,
@@ -206,7 +259,11 @@ class AttentionMixer:
             return self.out.partial(out)
         qkv = proj if part is None else ctx.new(T, width)
         vt = None
-        if self.own_kv:
+        if self.whole_norm:
+            kernels.proj_norm_store(qkv, nh * hd, nkv * hd, nkv * hdv, self.q_norm_weight,
+                                    self.k_norm_weight, eps, ctx.positions, view, ctx,
+                                    partial=part)
+        elif self.own_kv:
             if ctx.mode == PREFILL and kernels.attention_prefill_wants_transposed_values(
                     qkv, hd, hdv):
                 vt = kernels.prefill_values_scratch(T, ctx.batch, nkv, hd, qkv.device)
@@ -230,10 +287,10 @@ class AttentionMixer:
             else:
                 k, v, vt = ctx.step_kv[cache_entry]
             kernels.attention_prefill(q, k, v, out, ctx, nh, nkv, hd, s.scale, window, vt=vt,
-                                      value_dim=hdv, sinks=self.sinks)
+                                      value_dim=hdv, sinks=self.sinks, dist_bias=self.dist_bias)
         else:
             kernels.attention_decode(q, out, view, ctx, nh, nkv, hd, s.scale, window,
-                                     value_dim=hdv, sinks=self.sinks)
+                                     value_dim=hdv, sinks=self.sinks, dist_bias=self.dist_bias)
         return self.out.partial(out)
 
     def _attend_prompt(self, qkv: torch.Tensor, vt, ctx, cache_entry: int, writes_cache: bool,

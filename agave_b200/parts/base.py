@@ -47,11 +47,14 @@ class ParamSpec:
 class KVRequest:
     """Keys and values per position; ``window`` None keeps all of them, W keeps
     the last W.  ``value_dim``: the size of a value head where it differs from the
-    keys' ``head_dim`` (0: the same)."""
+    keys' ``head_dim`` (0: the same).  ``values_in_keys``: a position's value is the leading
+    ``value_dim`` elements of its key row, so the group holds one pool, not two (a latent that
+    serves as key and as value)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_dim: int = 0
+    values_in_keys: bool = False
 
 
 @dataclass(frozen=True)

@@ -4,6 +4,7 @@
     h += post_mixer_norm(mixer(pre_mixer_norm(h)))
     h += post_ffn_norm(ffn(pre_ffn_norm(h)))
 "pre": the same without the two post norms.
+"post": the same without the two pre norms: a branch reads the stream itself.
 ``residual_mult`` m: every branch joins as h += m * (...).  A spec without a feed-forward
 gives a layer of the mixer branch alone (and no norms of the second branch).
 
@@ -18,7 +19,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ..config.base import BlockSpec
+from ..config.base import BlockSpec, IdentityNormSpec
 from .base import ParamSpec, feed_forward_class, mixer_class, norm_class, register_block
 from .norm import fused_residual
 
@@ -26,15 +27,20 @@ from .norm import fused_residual
 class Block:
     def __init__(self, spec: BlockSpec, hidden_size: int, dtype: torch.dtype,
                  device: torch.device):
-        if spec.arrangement not in ("sandwich", "pre"):
+        if spec.arrangement not in ("sandwich", "pre", "post"):
             raise ValueError(f"unknown block arrangement {spec.arrangement!r}")
         self.spec, self.hidden_size, self.dtype, self.device = spec, hidden_size, dtype, device
         N = norm_class(spec.norm.kind)
-        self.sandwich = spec.arrangement == "sandwich"
+        self.sandwich = spec.arrangement in ("sandwich", "post")      # branches are normed
         self.mult = float(getattr(spec, "residual_mult", 1.0))
         has_ffn = spec.feed_forward is not None
-        self.pre_mixer_norm = N(spec.norm, hidden_size, dtype, device)
-        self.pre_ffn_norm = N(spec.norm, hidden_size, dtype, device) if has_ffn else None
+        # where a branch has no norm before it, the "identity" norm part stands in
+        P, pspec = N, spec.norm
+        if spec.arrangement == "post":
+            pspec = IdentityNormSpec()
+            P = norm_class(pspec.kind)
+        self.pre_mixer_norm = P(pspec, hidden_size, dtype, device)
+        self.pre_ffn_norm = P(pspec, hidden_size, dtype, device) if has_ffn else None
         self.post_mixer_norm = N(spec.norm, hidden_size, dtype, device) if self.sandwich else None
         self.post_ffn_norm = (N(spec.norm, hidden_size, dtype, device)
                               if self.sandwich and has_ffn else None)
@@ -46,8 +52,10 @@ class Block:
     def param_specs(cls, spec: BlockSpec, hidden_size: int) -> Dict[str, ParamSpec]:
         N = norm_class(spec.norm.kind)
         has_ffn = spec.feed_forward is not None
-        names = ["pre_mixer_norm"] + (["pre_ffn_norm"] if has_ffn else [])
-        if spec.arrangement == "sandwich":
+        names = []
+        if spec.arrangement != "post":
+            names += ["pre_mixer_norm"] + (["pre_ffn_norm"] if has_ffn else [])
+        if spec.arrangement != "pre":
             names += ["post_mixer_norm"] + (["post_ffn_norm"] if has_ffn else [])
         out: Dict[str, ParamSpec] = {}
         for n in names:

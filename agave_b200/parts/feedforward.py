@@ -14,7 +14,8 @@ from typing import Dict, Optional
 
 import torch
 
-from ..config.base import GatedFeedForwardSpec
+from .. import kernels
+from ..config.base import DenseFeedForwardSpec, GatedFeedForwardSpec
 from .base import ParamSpec, register_feed_forward
 from .linear import GatedLinear, Linear
 
@@ -48,3 +49,35 @@ class GatedFeedForward:
 
 
 register_feed_forward("gated_dense", GatedFeedForward)
+
+
+class DenseFeedForward:
+    """down(act(up x)): no gate.  "relu2" is the squared relu, max(z, 0)^2."""
+
+    def __init__(self, spec: DenseFeedForwardSpec, hidden_size: int, dtype: torch.dtype,
+                 device: torch.device):
+        if spec.activation != "relu2":
+            raise ValueError(f"dense feed-forward: unknown activation {spec.activation!r}")
+        self.spec, self.hidden_size = spec, hidden_size
+        self.up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    @classmethod
+    def param_specs(cls, spec: DenseFeedForwardSpec, hidden_size: int) -> Dict[str, ParamSpec]:
+        ff = spec.intermediate_size
+        return {"up_proj.weight": ParamSpec((ff, hidden_size)),
+                "down_proj.weight": ParamSpec((hidden_size, ff))}
+
+    def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype,
+             device: torch.device) -> None:
+        self.up = Linear(tensors["up_proj.weight"].to(device=device, dtype=dtype).contiguous(),
+                         role="up")
+        self.down = Linear(tensors["down_proj.weight"].to(device=device, dtype=dtype).contiguous(),
+                           role="down")
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        z = self.up.activated(x, self.spec.activation)
+        return self.down.partial(z)
+
+
+register_feed_forward("dense", DenseFeedForward)

@@ -31,6 +31,12 @@ class Linear:
         kernels.linear(x, self.weight, out, op=self.role)
         return out
 
+    def activated(self, x: torch.Tensor, activation: str) -> torch.Tensor:
+        """act(x w^T) in x's dtype ("relu2": the squared relu)."""
+        out = torch.empty((x.shape[0], self.out_features), dtype=x.dtype, device=x.device)
+        kernels.linear_activated(x, self.weight, out, activation, op=self.role)
+        return out
+
     def partial(self, x: torch.Tensor, cheap_sum: bool = False) -> torch.Tensor:
         """x w^T for a consumer that sums over a leading axis itself: [S, T, N]
         32-bit partial sums over ranges of K on the tensor-core path (S may be

@@ -16,7 +16,7 @@ from typing import Dict, Optional
 import torch
 
 from .. import kernels
-from ..config.base import LayerNormSpec, NormSpec
+from ..config.base import IdentityNormSpec, LayerNormSpec, NormSpec
 from .base import ParamSpec, register_norm
 
 
@@ -102,8 +102,12 @@ class LayerNorm:
         return out
 
     def residual(self, h: torch.Tensor, y: torch.Tensor, nxt, x_out, mult: float = 1.0) -> None:
-        """h += mult * self(y); x_out = nxt(h) if nxt (one launch when nxt is a layer norm)."""
-        if nxt is None or isinstance(nxt, LayerNorm):
+        """h += mult * self(y); x_out = nxt(h) if nxt (one launch when nxt is a layer norm or
+        no norm at all)."""
+        if isinstance(nxt, Identity):
+            kernels.layer_norm_join(h, y, self.weight, self.bias, None, None, x_out,
+                                    eps_post=self.eps, mult=mult)
+        elif nxt is None or isinstance(nxt, LayerNorm):
             kernels.layer_norm_join(
                 h, y, self.weight, self.bias, nxt.weight if nxt is not None else None,
                 nxt.bias if nxt is not None else None, x_out if nxt is not None else None,
@@ -120,5 +124,33 @@ class LayerNorm:
                                 eps_next=self.eps, mult=mult)
 
 
+class Identity:
+    """No norm: the part that follows reads the 32-bit stream itself, rounded to the compute
+    dtype.  It has no tensors; the same interface, so that a block can stand before or after
+    blocks with norms."""
+
+    def __init__(self, spec: IdentityNormSpec, width: int, dtype: torch.dtype,
+                 device: torch.device):
+        self.spec, self.width = spec, width
+
+    @classmethod
+    def param_specs(cls, spec: IdentityNormSpec, width: int) -> Dict[str, ParamSpec]:
+        return {}
+
+    def load(self, tensors: Dict[str, torch.Tensor], device: torch.device) -> None:
+        pass
+
+    def forward(self, h: torch.Tensor, out: torch.Tensor,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        kernels.layer_norm_join(h, None, None, None, None, None, out, rows=rows)
+        return out
+
+    def after_residual(self, h: torch.Tensor, y: torch.Tensor, x_out: torch.Tensor,
+                       mult: float = 1.0) -> None:
+        """h += mult * y; x_out = h."""
+        kernels.layer_norm_join(h, y, None, None, None, None, x_out, mult=mult)
+
+
+register_norm("identity", Identity)
 register_norm("rmsnorm", RMSNorm)
 register_norm("layernorm", LayerNorm)
