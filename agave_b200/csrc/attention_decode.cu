@@ -89,7 +89,14 @@ struct DecodeArgs {
     int max_pages, page, cap, nh, nkv, hd, window, n_splits, chunk;
     float scale;
     const float* sinks;        // [nh] sink logits (exp(sink) joins the denominator once), or null
+    const float* dist_bias;    // [n_dist, nh] added to the scaled score by distance, or null
+    int n_dist;
 };
+
+// The learned bias of head h for the key at position j seen from position p.
+__device__ __forceinline__ float distance_bias(const DecodeArgs& a, int p, int j, int h) {
+    return a.dist_bias[(size_t)min(p - j, a.n_dist - 1) * a.nh + h];
+}
 
 // What the sink of head h adds to a normaliser taken relative to the maximum m.
 __device__ __forceinline__ float sink_term(const DecodeArgs& a, int h, float m) {
@@ -295,7 +302,8 @@ attention_decode_split_kernel(DecodeArgs a) {
         }
 #pragma unroll
         for (int hh = 0; hh < AD_GC; ++hh) {
-            const float t = warp_sum(s[hh]) * a.scale;
+            float t = warp_sum(s[hh]) * a.scale;
+            if (a.dist_bias && hh < gc) t += distance_bias(a, p, j0 + r, h0 + hh);
             if (lane == 0 && hh < gc) sc[hh * CH + r] = t;
         }
     }
@@ -907,8 +915,11 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
             for (int e = 0; e < 4; ++e) {
                 const int key = warp * 16 + i * 8 + tig * 2 + (e & 1);
                 const int row = gid + (e >> 1) * 8;
-                Ss[row * DM_KEYS + key] =
-                    key >= nlo && key < n ? s[i][e] * a.scale : -INFINITY;
+                float sv = key >= nlo && key < n ? s[i][e] * a.scale : -INFINITY;
+                // (with a distance bias the tiles come by copies, so jt + key is the position)
+                if (!TMA && a.dist_bias && row < gc && key >= nlo && key < n)
+                    sv += distance_bias(a, p, jt + key, h0 + row);
+                Ss[row * DM_KEYS + key] = sv;
             }
     } else {
         // 8 keys: one load brings their chunks of 32 dims, two products into sums of
@@ -929,8 +940,11 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
         for (int e = 0; e < 4; ++e) {
             const int key = warp * 8 + tig * 2 + (e & 1);
             const int row = gid + (e >> 1) * 8;
-            Ss[row * DM_KEYS + key] = key >= nlo && key < n
+            float sv = key >= nlo && key < n
                 ? ((s[0][e] + s[1][e]) + (s[2][e] + s[3][e])) * a.scale : -INFINITY;
+            if (!TMA && a.dist_bias && row < gc && key >= nlo && key < n)
+                sv += distance_bias(a, p, jt + key, h0 + row);
+            Ss[row * DM_KEYS + key] = sv;
         }
     }
     __syncthreads();
@@ -1225,8 +1239,9 @@ int launch_decode_form(const DecodeArgs& a, int B, cudaStream_t stream, const Fu
     // 8,000 positions; 8 sequences of 256 to 4,096 with four kv heads of 256 32.6 -> 23.6;
     // 64 sequences with a ring of 512 12.5 -> 11.2; but one tile per CTA (8 sequences with
     // a ring of 512) 5.7 -> 6.1, which stays with the copies.
-    bool tma = can && form == 2;
-    if (can && form == 0) {
+    // (a distance bias wants every key's position, which the ring-counted TMA tiles do not give)
+    bool tma = can && form == 2 && !a.dist_bias;
+    if (can && form == 0 && !a.dist_bias) {
         const int G = a.nh / a.nkv, groups = a.nkv * ((G + DM_HEADS - 1) / DM_HEADS);
         int cs, clusters;
         const int most = most_tiles(a, true);
@@ -1279,8 +1294,11 @@ static int attention_decode_impl(const void* q, long long q_stride, void* out, i
                                  int cap, int B, int nh, int nkv, int hd, float scale, int window,
                                  int max_keys, float* part_acc, float* part_ml, int* counters,
                                  cudaStream_t stream, const FuseQK& fq,
-                                 const float* sinks = nullptr) {
+                                 const float* sinks = nullptr, const float* dist_bias = nullptr,
+                                 int n_dist = 0) {
     AGV_REQUIRE(B >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention_decode: bad sizes");
+    AGV_REQUIRE(!dist_bias || (n_dist > 0 && !fq.part), "attention_decode: a distance bias needs "
+                "its table and finished queries");
     AGV_REQUIRE(!fq.q_only || !fq.store_kv, "attention_decode: queries alone bring nothing to store");
     AGV_REQUIRE(fq.qt_coef == 0.f || fq.qt_every > 0, "attention_decode: the query temperature "
                 "needs a period >= 1");
@@ -1305,7 +1323,8 @@ static int attention_decode_impl(const void* q, long long q_stride, void* out, i
     AGV_REQUIRE(smem <= (size_t)AD_MAX_SMEM, "attention_decode: %zu bytes of shared memory needed",
                 smem);
     DecodeArgs a{q, q_stride, out, k_pool, v_pool, page_table, slots, positions, part_acc, part_ml,
-                 counters, max_pages, page, cap, nh, nkv, hd, window, n_splits, ch, scale, sinks};
+                 counters, max_pages, page, cap, nh, nkv, hd, window, n_splits, ch, scale, sinks,
+                 dist_bias, n_dist};
     if (dtype == AGV_BF16 && hd % 8 == 0 && hd <= 256 && ch == DM_KEYS &&
         (fq.part || (q_stride % 8 == 0 && agv_aligned(q, 16)))) {
         if (hd <= 64) return launch_decode_form<64>(a, B, stream, fq);
@@ -1359,6 +1378,21 @@ AGV_API int agv_attention_decode_ex(const void* q, long long q_stride, void* out
     return attention_decode_impl(q, q_stride, out, dtype, k_pool, v_pool, page_table, slots,
                                  positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,
                                  max_keys, part_acc, part_ml, counters, stream, FuseQK{}, sinks);
+}
+
+// The same with a learned bias by distance: dist_bias [n_dist, nh] is added to the scaled
+// score of the key at distance min(p - j, n_dist - 1), or null.
+AGV_API int agv_attention_decode_ex2(const void* q, long long q_stride, void* out, int dtype,
+                                     const void* k_pool, const void* v_pool, const int* page_table,
+                                     const int* slots, const int* positions, int max_pages, int page,
+                                     int cap, int B, int nh, int nkv, int hd, float scale, int window,
+                                     int max_keys, float* part_acc, float* part_ml, int* counters,
+                                     const float* sinks, const float* dist_bias, int n_dist,
+                                     cudaStream_t stream) {
+    return attention_decode_impl(q, q_stride, out, dtype, k_pool, v_pool, page_table, slots,
+                                 positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,
+                                 max_keys, part_acc, part_ml, counters, stream, FuseQK{}, sinks,
+                                 dist_bias, n_dist);
 }
 
 // Whether agv_attention_decode_fused takes these sizes: bfloat16, head sizes 64, 128,

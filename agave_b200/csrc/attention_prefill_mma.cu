@@ -84,7 +84,8 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
                              const __nv_bfloat16* __restrict__ v, long long kv_stride,
                              __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_seqlens,
                              int nh, int nkv, int hd, float scale_log2e, int window,
-                             const float* __restrict__ sinks) {
+                             const float* __restrict__ sinks, int hdv, long long v_stride,
+                             const float* __restrict__ dist_bias, int n_dist) {
     pdl_wait();
     pdl_launch_next();
     constexpr int FA_M = NW * 16, FA_THREADS = NW * 32;
@@ -104,7 +105,7 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
 
     const __nv_bfloat16* qb = q + (size_t)seq0 * q_stride + (size_t)h * hd;
     const __nv_bfloat16* kb = k + (size_t)seq0 * kv_stride + (size_t)g * hd;
-    const __nv_bfloat16* vb = v + (size_t)seq0 * kv_stride + (size_t)g * hd;
+    const __nv_bfloat16* vb = v + (size_t)seq0 * v_stride + (size_t)g * hdv;
 
     // visible key range of this query tile: causal end, window start
     const int j_hi = min(m0 + FA_M - 1, len - 1);
@@ -114,7 +115,7 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
     load_tile<HDP, FA_M, FA_THREADS>(Qs, qb, q_stride, m0, len, hd);
     load_tile<HDP, FA_N, FA_THREADS>(Ks, kb, kv_stride, t_lo * FA_N, len, hd);
     cp_commit();
-    load_tile<HDP, FA_N, FA_THREADS>(Vs, vb, kv_stride, t_lo * FA_N, len, hd);
+    load_tile<HDP, FA_N, FA_THREADS>(Vs, vb, v_stride, t_lo * FA_N, len, hdv);
     cp_commit();
 
     float o[HDP / 8][4];
@@ -157,7 +158,13 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
                 const int j = j0 + i * 8 + tig * 2 + (e & 1);
                 const int p = qrow + (e >> 1) * 8;
                 const bool ok = j <= p && j < len && (window <= 0 || j > p - window);
-                const float val = ok ? s[i][e] * scale_log2e : -INFINITY;
+                float val = -INFINITY;
+                if (ok) {
+                    val = s[i][e] * scale_log2e;
+                    // a learned bias by distance, on the same base-2 scale as the score
+                    if (dist_bias)
+                        val += dist_bias[(size_t)min(p - j, n_dist - 1) * nh + h] * 1.4426950408889634f;
+                }
                 s[i][e] = val;
                 mx[e >> 1] = fmaxf(mx[e >> 1], val);
             }
@@ -203,7 +210,7 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
             }
         }
         __syncthreads();                                // every warp is done with this V tile
-        if (t < t_hi) load_tile<HDP, FA_N, FA_THREADS>(Vs, vb, kv_stride, (t + 1) * FA_N, len, hd);
+        if (t < t_hi) load_tile<HDP, FA_N, FA_THREADS>(Vs, vb, v_stride, (t + 1) * FA_N, len, hdv);
         cp_commit();
     }
     // ---- normalise and store
@@ -221,16 +228,16 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
     }
     const float inv0 = row_l[0] > 0.f ? 1.0f / row_l[0] : 0.f;
     const float inv1 = row_l[1] > 0.f ? 1.0f / row_l[1] : 0.f;
-    __nv_bfloat16* ob = out + (size_t)seq0 * (size_t)(nh * hd) + (size_t)h * hd;
+    __nv_bfloat16* ob = out + (size_t)seq0 * (size_t)(nh * hdv) + (size_t)h * hdv;
 #pragma unroll
     for (int i = 0; i < HDP / 8; ++i) {
         const int d = i * 8 + tig * 2;
-        if (d < hd) {
+        if (d < hdv) {
             if (qrow < len)
-                *reinterpret_cast<unsigned*>(ob + (size_t)qrow * (nh * hd) + d) =
+                *reinterpret_cast<unsigned*>(ob + (size_t)qrow * (nh * hdv) + d) =
                     pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
             if (qrow + 8 < len)
-                *reinterpret_cast<unsigned*>(ob + (size_t)(qrow + 8) * (nh * hd) + d) =
+                *reinterpret_cast<unsigned*>(ob + (size_t)(qrow + 8) * (nh * hdv) + d) =
                     pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
         }
     }
@@ -239,7 +246,8 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
 template <int HDP, int NW>
 int launch_fa(const void* q, long long q_stride, const void* k, const void* v, long long kv_stride,
               void* out, const int* cu_seqlens, int B, int max_len, int nh, int nkv, int hd,
-              float scale, int window, cudaStream_t stream, const float* sinks) {
+              float scale, int window, cudaStream_t stream, const float* sinks, int hdv,
+              long long v_stride, const float* dist_bias, int n_dist) {
     auto kern = attention_prefill_mma_kernel<HDP, NW>;
     constexpr int FA_M = NW * 16, FA_THREADS = NW * 32;
     constexpr int smem = (FA_M + 2 * FA_N) * HDP * 2;
@@ -251,7 +259,7 @@ int launch_fa(const void* q, long long q_stride, const void* k, const void* v, l
     dim3 grid((max_len + FA_M - 1) / FA_M, nh, B);
     agv_launch(kern, grid, FA_THREADS, smem, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
         kv_stride, (__nv_bfloat16*)out, cu_seqlens, nh, nkv, hd,
-        scale * 1.4426950408889634f, window, sinks);
+        scale * 1.4426950408889634f, window, sinks, hdv, v_stride, dist_bias, n_dist);
     AGV_LAUNCH_OK("attention_prefill_mma_kernel");
     return 0;
 }
@@ -269,12 +277,19 @@ AGV_API int agv_attention_prefill_mma_supported(int hd, long long q_stride, long
 // dense; cu_seqlens: [B + 1] first token of each sequence; max_len: the
 // greatest sequence length (sizes the grid).  window 0: no window.
 // sinks: [nh] sink logits (exp(sink) joins each row's softmax denominator once), or null.
-AGV_API int agv_attention_prefill_mma_ex(const void* q, long long q_stride, const void* k,
-                                         const void* v, long long kv_stride, void* out,
-                                         const int* cu_seqlens, int B, int max_len, int nh, int nkv,
-                                         int hd, float scale, int window, const float* sinks,
-                                         cudaStream_t stream) {
+// hdv / v_stride: the value head size and the value rows' stride where they differ from the
+// keys' (out is then [T, nh * hdv]); dist_bias [n_dist, nh]: added to the scaled score of a key
+// at distance min(t - j, n_dist - 1), or null.
+AGV_API int agv_attention_prefill_mma_ex2(const void* q, long long q_stride, const void* k,
+                                          const void* v, long long kv_stride, void* out,
+                                          const int* cu_seqlens, int B, int max_len, int nh, int nkv,
+                                          int hd, float scale, int window, const float* sinks,
+                                          int hdv, long long v_stride, const float* dist_bias,
+                                          int n_dist, cudaStream_t stream) {
     AGV_REQUIRE(B >= 0 && nh > 0 && nkv > 0 && hd > 0 && max_len >= 0, "attention: bad sizes");
+    AGV_REQUIRE(hdv > 0 && hdv % 8 == 0 && hdv <= 256 && v_stride % 8 == 0,
+                "attention: the value head size (%d) must be a multiple of 8 up to 256", hdv);
+    AGV_REQUIRE(!dist_bias || n_dist > 0, "attention: an empty distance table");
     AGV_REQUIRE(nh % nkv == 0, "attention: %d heads are not a multiple of %d kv heads", nh, nkv);
     AGV_REQUIRE(agv_attention_prefill_mma_supported(hd, q_stride, kv_stride),
                 "attention: the tensor-core kernel needs head_dim (%d) a multiple of 8 up to 256 "
@@ -289,13 +304,26 @@ AGV_API int agv_attention_prefill_mma_ex(const void* q, long long q_stride, cons
     const bool wide = false;
 #define AGV_FA(HDP)                                                                             \
     return wide ? launch_fa<HDP, 8>(q, q_stride, k, v, kv_stride, out, cu_seqlens, B, max_len,  \
-                                    nh, nkv, hd, scale, window, stream, sinks)                   \
+                                    nh, nkv, hd, scale, window, stream, sinks, hdv, v_stride,    \
+                                    dist_bias, n_dist)                                           \
                 : launch_fa<HDP, 4>(q, q_stride, k, v, kv_stride, out, cu_seqlens, B, max_len,  \
-                                    nh, nkv, hd, scale, window, stream, sinks)
-    if (hd <= 64) AGV_FA(64);
-    if (hd <= 128) AGV_FA(128);
+                                    nh, nkv, hd, scale, window, stream, sinks, hdv, v_stride,    \
+                                    dist_bias, n_dist)
+    const int widest = hd > hdv ? hd : hdv;
+    if (widest <= 64) AGV_FA(64);
+    if (widest <= 128) AGV_FA(128);
     AGV_FA(256);
 #undef AGV_FA
+}
+
+AGV_API int agv_attention_prefill_mma_ex(const void* q, long long q_stride, const void* k,
+                                         const void* v, long long kv_stride, void* out,
+                                         const int* cu_seqlens, int B, int max_len, int nh, int nkv,
+                                         int hd, float scale, int window, const float* sinks,
+                                         cudaStream_t stream) {
+    return agv_attention_prefill_mma_ex2(q, q_stride, k, v, kv_stride, out, cu_seqlens, B, max_len,
+                                         nh, nkv, hd, scale, window, sinks, hd, kv_stride, nullptr,
+                                         0, stream);
 }
 
 AGV_API int agv_attention_prefill_mma(const void* q, long long q_stride, const void* k,

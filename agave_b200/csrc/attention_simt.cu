@@ -19,7 +19,7 @@
 #include "common.cuh"
 
 constexpr int AT_WARPS = 4;
-constexpr int AT_MAX_I = 16;          // head_dim <= 32 * AT_MAX_I
+constexpr int AT_MAX_I = 24;          // head_dim <= 32 * AT_MAX_I
 
 struct PagedKV {
     const void* k_pool;        // [n_pages, page, n_kv, hd] of this layer

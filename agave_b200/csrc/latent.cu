@@ -223,7 +223,7 @@ template <typename T, typename TO>
 __global__ void __launch_bounds__(HL_WARPS * 32)
 heads_linear_kernel(const T* __restrict__ x, long long ldx, long long xs, const T* __restrict__ W,
                     TO* __restrict__ out, long long ldo, long long os, int n_tokens, int N, int K,
-                    int rows_per_cta) {
+                    int rows_per_cta, int tail) {
     extern __shared__ float xsh[];           // [HL_TOK, K]
     const int a = blockIdx.y;
     const int t0 = blockIdx.z * HL_TOK;
@@ -236,6 +236,13 @@ heads_linear_kernel(const T* __restrict__ x, long long ldx, long long xs, const 
         xsh[e] = to_f32(x[(size_t)(t0 + tt) * ldx + (size_t)a * xs + k]);
     }
     __syncthreads();
+    // the values that follow a head's K inputs pass through to behind its N outputs
+    if (tail > 0 && blockIdx.x == 0)
+        for (int e = threadIdx.x; e < nt * tail; e += blockDim.x) {
+            const int tt = e / tail, i = e % tail;
+            out[(size_t)(t0 + tt) * ldo + (size_t)a * os + N + i] =
+                from_f32<TO>(to_f32(x[(size_t)(t0 + tt) * ldx + (size_t)a * xs + K + i]));
+        }
     const int n_lo = blockIdx.x * rows_per_cta;
     const int n_hi = min(N, n_lo + rows_per_cta);
     for (int n = n_lo + warp; n < n_hi; n += HL_WARPS) {
@@ -438,11 +445,13 @@ AGV_API int agv_assemble_keys(const void* k_plain, long long ldp, const void* kr
 }
 
 // x: [T, heads, K] (row stride ldx, head stride xs); W: [heads, N, K] dense; out: [T, heads, N]
-// (row stride ldo, head stride os), in dtype or, with out_f32, 32-bit.
+// (row stride ldo, head stride os), in dtype or, with out_f32, 32-bit.  tail > 0: the tail
+// values x[t, a, K .. K + tail) are copied to out[t, a, N .. N + tail).
 AGV_API int agv_heads_linear(const void* x, long long ldx, long long xs, const void* W, void* out,
                              long long ldo, long long os, int dtype, int out_f32, int T,
-                             int heads, int N, int K, cudaStream_t stream) {
-    AGV_REQUIRE(T >= 0 && heads > 0 && N > 0 && K > 0, "heads_linear: bad sizes");
+                             int heads, int N, int K, int tail, cudaStream_t stream) {
+    AGV_REQUIRE(T >= 0 && heads > 0 && N > 0 && K > 0 && tail >= 0, "heads_linear: bad sizes");
+    AGV_REQUIRE(xs >= K + tail && os >= N + tail, "heads_linear: heads overlap");
     AGV_REQUIRE(heads <= 65535, "heads_linear: too many heads");
     AGV_REQUIRE((size_t)HL_TOK * K * 4 <= 48 * 1024, "heads_linear: K = %d too long", K);
     if (T == 0) return 0;
@@ -456,15 +465,15 @@ AGV_API int agv_heads_linear(const void* x, long long ldx, long long xs, const v
     if (dtype == AGV_F32)
         agv_launch(heads_linear_kernel<float, float>, grid, HL_WARPS * 32, smem, stream,
                    (const float*)x, ldx, xs, (const float*)W, (float*)out, ldo, os, T, N, K,
-                   rows_per_cta);
+                   rows_per_cta, tail);
     else if (dtype == AGV_BF16 && out_f32)
         agv_launch(heads_linear_kernel<__nv_bfloat16, float>, grid, HL_WARPS * 32, smem, stream,
                    (const __nv_bfloat16*)x, ldx, xs, (const __nv_bfloat16*)W, (float*)out, ldo, os,
-                   T, N, K, rows_per_cta);
+                   T, N, K, rows_per_cta, tail);
     else if (dtype == AGV_BF16)
         agv_launch(heads_linear_kernel<__nv_bfloat16, __nv_bfloat16>, grid, HL_WARPS * 32, smem,
                    stream, (const __nv_bfloat16*)x, ldx, xs, (const __nv_bfloat16*)W,
-                   (__nv_bfloat16*)out, ldo, os, T, N, K, rows_per_cta);
+                   (__nv_bfloat16*)out, ldo, os, T, N, K, rows_per_cta, tail);
     else return agv_fail(-1, "heads_linear: unknown dtype %d", dtype);
     AGV_LAUNCH_OK("heads_linear_kernel");
     return 0;

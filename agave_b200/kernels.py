@@ -685,12 +685,15 @@ def assemble_keys(k_plain: torch.Tensor, kr: torch.Tensor, k_out: torch.Tensor, 
                                            dtype_code(k_out.dtype), T, heads, d, r, _stream()))
 
 
-def heads_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, op: str = "heads_linear") -> None:
-    """out[t, a, :] = w[a] x[t, a, :]: x [T, heads, K] and out [T, heads, N] are views with
-    unit innermost stride, w [heads, N, K] dense; out in x's dtype or 32-bit."""
+def heads_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tail: int = 0,
+                 op: str = "heads_linear") -> None:
+    """out[t, a, :N] = w[a] x[t, a, :K]: x [T, heads, K + tail] and out [T, heads, N + tail] are
+    views with unit innermost stride, w [heads, N, K] dense; out in x's dtype or 32-bit.  The
+    ``tail`` values behind a head's inputs are copied behind its outputs."""
     T, A, K = x.shape
+    K -= tail
     N = w.shape[1]
-    assert w.shape == (A, N, K) and out.shape == (T, A, N) and x.dtype == w.dtype
+    assert w.shape == (A, N, K) and out.shape == (T, A, N + tail) and x.dtype == w.dtype
     assert x.stride(2) == 1 and out.stride(2) == 1
     _dense(w, "w")
     out_f32 = out.dtype == torch.float32 and x.dtype != torch.float32
@@ -699,7 +702,7 @@ def heads_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, op: str = 
         _check(library().agv_heads_linear(
             _ptr(x), ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(x.stride(1)), _ptr(w),
             _ptr(out), ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out.stride(1)),
-            dtype_code(x.dtype), 1 if out_f32 else 0, T, A, N, K, _stream()))
+            dtype_code(x.dtype), 1 if out_f32 else 0, T, A, N, K, int(tail), _stream()))
 
 
 def gate_sigmoid(out: torch.Tensor, g: torch.Tensor) -> None:
@@ -1053,19 +1056,25 @@ def gemv_few(w: torch.Tensor, out: torch.Tensor, x: Optional[torch.Tensor] = Non
 def attention_prefill_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
                           cu_seqlens: torch.Tensor, max_len: int, n_heads: int, n_kv_heads: int,
                           head_dim: int, scale: float, window: int,
-                          sinks: Optional[torch.Tensor] = None) -> None:
+                          sinks: Optional[torch.Tensor] = None, value_dim: int = 0,
+                          dist_bias: Optional[torch.Tensor] = None) -> None:
     """Prompts that start at 0 on the tensor cores (bfloat16, head sizes in steps
-    of 8 up to 256); q, k, v are row-strided views, out is dense."""
-    _f32(sinks, "sinks")
+    of 8 up to 256); q, k, v are row-strided views, out is dense.  ``value_dim``: the value
+    head size where it differs from the keys'; ``dist_bias`` [n, nh]: see
+    ``attention_prefill_simt``."""
+    _f32(sinks, "sinks"); _f32(dist_bias, "dist_bias")
     assert q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype
     assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1
-    assert k.stride(0) == v.stride(0)
     _dense(out, "out"); _i32(cu_seqlens, "cu_seqlens")
-    _check(library().agv_attention_prefill_mma_ex(
+    if dist_bias is not None:
+        _dense(dist_bias, "dist_bias")
+        assert dist_bias.dim() == 2 and dist_bias.shape[1] == n_heads
+    _check(library().agv_attention_prefill_mma_ex2(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), _ptr(v),
         ctypes.c_longlong(k.stride(0)), _ptr(out), _ptr(cu_seqlens), cu_seqlens.numel() - 1,
         max_len, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window, _ptr(sinks),
-        _stream()))
+        value_dim or head_dim, ctypes.c_longlong(v.stride(0)), _ptr(dist_bias),
+        dist_bias.shape[0] if dist_bias is not None else 0, _stream()))
 
 
 def prefill_values_scratch(T: int, B: int, n_kv_heads: int, head_dim: int,
@@ -1143,18 +1152,20 @@ def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, w
     (and for value heads of another size than the keys') the one-warp-per-(token, head)
     kernel.  ``sinks`` [nh]: a logit per query head that joins its denominator once."""
     hdv = value_dim or head_dim
-    aligned = (q.dtype == torch.bfloat16 and head_dim <= 256 and hdv == head_dim and
-               dist_bias is None and k.stride(0) == v.stride(0) and
-               q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and
-               k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0)
+    aligned = (q.dtype == torch.bfloat16 and head_dim <= 256 and hdv <= 256 and
+               q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 and v.stride(0) % 8 == 0 and
+               q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0)
+    # the tcgen05 kernel knows neither value heads of their own size nor a distance bias
+    same = hdv == head_dim and dist_bias is None and k.stride(0) == v.stride(0)
     with _span("attention", *_attention_cost(ctx, q, k, v, out, n_heads, head_dim, window)):
-        if (aligned and head_dim % 16 == 0 and _PREFILL_TC and scale > 0 and
+        if (aligned and same and head_dim % 16 == 0 and _PREFILL_TC and scale > 0 and
                 q.shape[0] > PREFILL_TC_MIN_TOKENS):
             attention_prefill_tc(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads, n_kv_heads,
                                  head_dim, scale, window, vt=vt, sinks=sinks)
-        elif aligned and head_dim % 8 == 0:
+        elif aligned and head_dim % 8 == 0 and hdv % 8 == 0:
             attention_prefill_mma(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads,
-                                  n_kv_heads, head_dim, scale, window, sinks=sinks)
+                                  n_kv_heads, head_dim, scale, window, sinks=sinks,
+                                  value_dim=hdv, dist_bias=dist_bias)
         else:
             attention_prefill_simt(q, k, v, out, ctx.positions, ctx.seq_index, ctx.cu_seqlens,
                                    n_heads, n_kv_heads, head_dim, scale, window, value_dim=hdv,
@@ -1238,7 +1249,8 @@ def attention_decode_split(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Ten
                            n_kv_heads: int, head_dim: int, scale: float, window: int,
                            max_keys: int, part_acc: Optional[torch.Tensor] = None,
                            part_ml: Optional[torch.Tensor] = None,
-                           sinks: Optional[torch.Tensor] = None) -> None:
+                           sinks: Optional[torch.Tensor] = None,
+                           dist_bias: Optional[torch.Tensor] = None) -> None:
     """One query per batch entry against the paged cache, keys split into chunks
     whose partial results go through scratch memory (allocated here if not given)."""
     B = q.shape[0]
@@ -1256,12 +1268,16 @@ def attention_decode_split(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Ten
     assert part_ml.numel() >= B * n_heads * n_splits * 2
     _f32(part_acc, "part_acc"); _f32(part_ml, "part_ml")
     counters = _decode_counters(q.device, B * n_heads)
-    _f32(sinks, "sinks")
-    _check(library().agv_attention_decode_ex(
+    _f32(sinks, "sinks"); _f32(dist_bias, "dist_bias")
+    if dist_bias is not None:
+        _dense(dist_bias, "dist_bias")
+        assert dist_bias.dim() == 2 and dist_bias.shape[1] == n_heads
+    _check(library().agv_attention_decode_ex2(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(out), dtype_code(q.dtype), _ptr(k_pool),
         _ptr(v_pool), _ptr(page_table), _ptr(slots), _ptr(positions), page_table.shape[1], page,
         cap, B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window, max_keys,
-        _ptr(part_acc), _ptr(part_ml), _ptr(counters), _ptr(sinks), _stream()))
+        _ptr(part_acc), _ptr(part_ml), _ptr(counters), _ptr(sinks), _ptr(dist_bias),
+        dist_bias.shape[0] if dist_bias is not None else 0, _stream()))
 
 
 _FUSED_DECODE = os.environ.get("AGAVE_B200_FUSED_DECODE_ATTENTION", "1") != "0"
@@ -1325,12 +1341,12 @@ def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, wi
     hdv = value_dim or head_dim
     with _span("attention", *_attention_cost(ctx, q, None, None, out, n_heads, head_dim, window,
                                              n_kv_heads)):
-        if (head_dim % 16 == 0 and head_dim <= 512 and hdv == head_dim and dist_bias is None
-                and not values_in_keys):
+        if head_dim % 16 == 0 and head_dim <= 512 and hdv == head_dim and not values_in_keys:
             max_keys = min(window, ctx.max_len) if window else ctx.max_len
             attention_decode_split(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
                                    ctx.positions, view.page, view.cap, n_heads, n_kv_heads,
-                                   head_dim, scale, window, max(1, max_keys), sinks=sinks)
+                                   head_dim, scale, window, max(1, max_keys), sinks=sinks,
+                                   dist_bias=dist_bias)
         else:
             attention_paged_simt(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
                                  ctx.positions, ctx.seq_index, view.page, view.cap, n_heads,

@@ -134,15 +134,23 @@ class LatentAttentionMixer:
             kernels.attention_prefill(q, k, kv[:, A * d:], out, ctx, A, A, hw, s.scale, 0,
                                       value_dim=dv)
         else:
-            # the key up-projection goes into the query; the heads attend to the cache rows
-            ql = ctx.new(T, A, R + r)
-            q3 = q.view(T, A, hw) if q.is_contiguous() else q.unflatten(1, (A, hw))
-            kernels.heads_linear(q3[:, :, :d], self.k_absorb, ql[:, :, :R], op="q_absorb")
-            ql[:, :, R:].copy_(q3[:, :, d:])
-            lat = ctx.new(T, A * R)
-            kernels.attention_decode(ql.view(T, A * (R + r)), lat, view, ctx, A, 1, R + r, s.scale,
-                                     0, value_dim=R, values_in_keys=True)
-            kernels.heads_linear(lat.view(T, A, R), self.v_up, out.view(T, A, dv), op="v_up")
+            # the key up-projection goes into the query (the rotated part passes through);
+            # the heads attend to the cache rows themselves
+            D = R + r
+            ql = ctx.new(T, A, D)
+            kernels.heads_linear(q.unflatten(1, (A, hw)), self.k_absorb, ql, tail=r, op="q_absorb")
+            if D % 16 == 0 and D <= 512:
+                # the split kernel with the whole row as the value: one kv head, every query
+                # head in its group; the r values behind the latent's weighted sum are unused
+                lat = ctx.new(T, A, D)
+                kernels.attention_decode(ql.view(T, A * D), lat.view(T, A * D), view, ctx, A, 1, D,
+                                         s.scale, 0)
+                lat = lat[:, :, :R]
+            else:
+                lat = ctx.new(T, A, R)
+                kernels.attention_decode(ql.view(T, A * D), lat.view(T, A * R), view, ctx, A, 1, D,
+                                         s.scale, 0, value_dim=R, values_in_keys=True)
+            kernels.heads_linear(lat, self.v_up, out.view(T, A, dv), op="v_up")
         if G:
             kernels.gate_sigmoid(out, row[:, Q + R + r:])
         return self.out.partial(out)
