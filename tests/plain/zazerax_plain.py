@@ -111,15 +111,16 @@ def softmax_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: 
     T, A, _ = q.shape
     rep = A // k.shape[1]
     out = torch.zeros(T, A, v.shape[2], dtype=q.dtype)
+    if bias is not None:
+        row_of = torch.tensor([distance_bucket(n, bias.shape[0], far) for n in range(T)])
     for a in range(A):
         g = a // rep
         for t in range(T):
             lo = 0 if window is None else max(0, t - window + 1)
             s = (k[lo:t + 1, g] @ q[t, a]) * scale
             if bias is not None:
-                rows = bias.shape[0]
-                s = s + torch.stack([bias[distance_bucket(t - j, rows, far), a]
-                                     for j in range(lo, t + 1)])
+                # keys lo..t lie at distances t - lo .. 0
+                s = s + bias[row_of[:t - lo + 1].flip(0), a]
             m = s.max()
             if one_in_denominator:
                 m = torch.clamp(m, min=0.0)
