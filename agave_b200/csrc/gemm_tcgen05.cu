@@ -361,6 +361,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                         float v = __uint_as_float(r[j]);
                         if (GATED)
                             v = (act == 1 ? silu_fast(v) : gelu_tanh_fast(v)) * __uint_as_float(u[j]);
+                        else if (MODE == 0 && act == 2) { v = fmaxf(v, 0.f); v *= v; }   // squared relu
                         store_out<TO>(ctile + (c + j) * TILE_M + fl, v);
                     }
                 }
@@ -444,6 +445,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                         if (HALF) up += inbox[((size_t)q * BN + n) * rows + per + jl];
                     }
                     if (HALF) acc = (act == 1 ? silu_fast(acc) : gelu_tanh_fast(acc)) * up;
+                    else if (MODE == 0 && act == 2) { acc = fmaxf(acc, 0.f); acc *= acc; }
                     store_out<TO>(gout + (size_t)(n0 + n) * ldc + m0 + fl, acc);
                 }
             }
@@ -470,6 +472,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
                         for (int q = 0; q < 8; ++q) up += pu[q];
                         acc = (act == 1 ? silu_fast(acc) : gelu_tanh_fast(acc)) * up;
+                    } else if (MODE == 0 && act == 2) {
+                        acc = fmaxf(acc, 0.f);
+                        acc *= acc;
                     }
                     store_out<TO>(gout + (size_t)(n0 + n) * ldc + m0 + fl, acc);
                 }
@@ -923,6 +928,13 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                             store_out<TO>(wst + j * 32 + lane,
                                           gelu_tanh_fast(__uint_as_float(r[j])) *
                                               __uint_as_float(u[j]));
+                    }
+                } else if (MODE == 0 && act == 2) {
+                    // plain product with the squared relu on it
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float v = fmaxf(__uint_as_float(r[j]), 0.f);
+                        store_out<TO>(wst + j * 32 + lane, v * v);
                     }
                 } else {
 #pragma unroll
@@ -1435,6 +1447,10 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
                 "linear: operands must be 16-byte aligned");
     AGV_REQUIRE(lda >= K && ldc >= N, "linear: row strides shorter than rows");
     AGV_REQUIRE(splits >= 1, "linear: splits must be >= 1");
+    // act 2 (the squared relu) belongs to the plain product and needs a finished sum
+    AGV_REQUIRE(act != 2 || (!w2 && (splits == 1 || splits == cluster)),
+                "linear: the squared relu goes with a plain product whose sum is finished in the "
+                "kernel (one range of K, or one cluster's)");
     AGV_REQUIRE(splits == 1 || !w2 || (cluster == splits && T <= 64),
                 "linear: the gated form splits K only over one cluster and for at most 64 tokens");
     AGV_REQUIRE(cluster == 0 || (cluster >= 2 && cluster <= 8 && splits % cluster == 0),

@@ -223,7 +223,8 @@ template <typename T, typename TO>
 __global__ void __launch_bounds__(HL_WARPS * 32)
 heads_linear_kernel(const T* __restrict__ x, long long ldx, long long xs, const T* __restrict__ W,
                     TO* __restrict__ out, long long ldo, long long os, int n_tokens, int N, int K,
-                    int rows_per_cta, int tail) {
+                    int rows_per_cta, int tail, const T* __restrict__ gate, long long ldg,
+                    int gate_per_head) {
     extern __shared__ float xsh[];           // [HL_TOK, K]
     const int a = blockIdx.y;
     const int t0 = blockIdx.z * HL_TOK;
@@ -259,8 +260,16 @@ heads_linear_kernel(const T* __restrict__ x, long long ldx, long long xs, const 
 #pragma unroll
         for (int tt = 0; tt < HL_TOK; ++tt) {
             if (tt < nt) {
-                const float s = warp_sum(acc[tt]);
-                if (lane == 0) out[(size_t)(t0 + tt) * ldo + (size_t)a * os + n] = from_f32<TO>(s);
+                float s = warp_sum(acc[tt]);
+                if (lane == 0) {
+                    if (gate) {
+                        // an output gate: sigmoid of one logit per head, or per output value
+                        const float z = to_f32(gate[(size_t)(t0 + tt) * ldg +
+                                                    (gate_per_head ? a : a * N + n)]);
+                        s /= 1.0f + expf(-z);
+                    }
+                    out[(size_t)(t0 + tt) * ldo + (size_t)a * os + n] = from_f32<TO>(s);
+                }
             }
         }
     }
@@ -446,10 +455,13 @@ AGV_API int agv_assemble_keys(const void* k_plain, long long ldp, const void* kr
 
 // x: [T, heads, K] (row stride ldx, head stride xs); W: [heads, N, K] dense; out: [T, heads, N]
 // (row stride ldo, head stride os), in dtype or, with out_f32, 32-bit.  tail > 0: the tail
-// values x[t, a, K .. K + tail) are copied to out[t, a, N .. N + tail).
+// values x[t, a, K .. K + tail) are copied to out[t, a, N .. N + tail).  gate (may be null):
+// logits [T, heads] (gate_per_head) or [T, heads * N] with row stride ldg; an output is
+// multiplied by the sigmoid of its logit.
 AGV_API int agv_heads_linear(const void* x, long long ldx, long long xs, const void* W, void* out,
                              long long ldo, long long os, int dtype, int out_f32, int T,
-                             int heads, int N, int K, int tail, cudaStream_t stream) {
+                             int heads, int N, int K, int tail, const void* gate, long long ldg,
+                             int gate_per_head, cudaStream_t stream) {
     AGV_REQUIRE(T >= 0 && heads > 0 && N > 0 && K > 0 && tail >= 0, "heads_linear: bad sizes");
     AGV_REQUIRE(xs >= K + tail && os >= N + tail, "heads_linear: heads overlap");
     AGV_REQUIRE(heads <= 65535, "heads_linear: too many heads");
@@ -465,15 +477,16 @@ AGV_API int agv_heads_linear(const void* x, long long ldx, long long xs, const v
     if (dtype == AGV_F32)
         agv_launch(heads_linear_kernel<float, float>, grid, HL_WARPS * 32, smem, stream,
                    (const float*)x, ldx, xs, (const float*)W, (float*)out, ldo, os, T, N, K,
-                   rows_per_cta, tail);
+                   rows_per_cta, tail, (const float*)gate, ldg, gate_per_head);
     else if (dtype == AGV_BF16 && out_f32)
         agv_launch(heads_linear_kernel<__nv_bfloat16, float>, grid, HL_WARPS * 32, smem, stream,
                    (const __nv_bfloat16*)x, ldx, xs, (const __nv_bfloat16*)W, (float*)out, ldo, os,
-                   T, N, K, rows_per_cta, tail);
+                   T, N, K, rows_per_cta, tail, (const __nv_bfloat16*)gate, ldg, gate_per_head);
     else if (dtype == AGV_BF16)
         agv_launch(heads_linear_kernel<__nv_bfloat16, __nv_bfloat16>, grid, HL_WARPS * 32, smem,
                    stream, (const __nv_bfloat16*)x, ldx, xs, (const __nv_bfloat16*)W,
-                   (__nv_bfloat16*)out, ldo, os, T, N, K, rows_per_cta, tail);
+                   (__nv_bfloat16*)out, ldo, os, T, N, K, rows_per_cta, tail,
+                   (const __nv_bfloat16*)gate, ldg, gate_per_head);
     else return agv_fail(-1, "heads_linear: unknown dtype %d", dtype);
     AGV_LAUNCH_OK("heads_linear_kernel");
     return 0;

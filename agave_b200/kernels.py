@@ -18,7 +18,7 @@ from . import perf as _perf_mod
 from .csrc import build as _build
 
 F32, BF16 = 0, 1
-ACT = {"gelu_tanh": 0, "silu": 1}
+ACT = {"gelu_tanh": 0, "silu": 1, "relu2": 2}     # relu2: on a plain product only
 
 _lib = None
 _lock = threading.Lock()
@@ -686,10 +686,11 @@ def assemble_keys(k_plain: torch.Tensor, kr: torch.Tensor, k_out: torch.Tensor, 
 
 
 def heads_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tail: int = 0,
-                 op: str = "heads_linear") -> None:
+                 gate: Optional[torch.Tensor] = None, op: str = "heads_linear") -> None:
     """out[t, a, :N] = w[a] x[t, a, :K]: x [T, heads, K + tail] and out [T, heads, N + tail] are
     views with unit innermost stride, w [heads, N, K] dense; out in x's dtype or 32-bit.  The
-    ``tail`` values behind a head's inputs are copied behind its outputs."""
+    ``tail`` values behind a head's inputs are copied behind its outputs.  ``gate`` [T, heads]
+    or [T, heads * N]: every output is multiplied by the sigmoid of its (head's) logit."""
     T, A, K = x.shape
     K -= tail
     N = w.shape[1]
@@ -698,11 +699,16 @@ def heads_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tail: int 
     _dense(w, "w")
     out_f32 = out.dtype == torch.float32 and x.dtype != torch.float32
     assert out_f32 or out.dtype == x.dtype
+    per_head = 0
+    if gate is not None:
+        assert gate.shape in ((T, A), (T, A * N)) and gate.stride(1) == 1 and gate.dtype == x.dtype
+        per_head = 1 if gate.shape[1] == A and N != 1 else 0
     with _span(op, _nbytes(w, x, out), 2 * T * A * N * K):
         _check(library().agv_heads_linear(
             _ptr(x), ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(x.stride(1)), _ptr(w),
             _ptr(out), ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out.stride(1)),
-            dtype_code(x.dtype), 1 if out_f32 else 0, T, A, N, K, int(tail), _stream()))
+            dtype_code(x.dtype), 1 if out_f32 else 0, T, A, N, K, int(tail), _ptr(gate),
+            ctypes.c_longlong(gate.stride(0) if gate is not None else 0), per_head, _stream()))
 
 
 def gate_sigmoid(out: torch.Tensor, g: torch.Tensor) -> None:
@@ -730,8 +736,16 @@ def linear_activated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, activa
     """out = act(x w^T); "relu2" is the squared relu."""
     if activation != "relu2":
         raise KernelError(f"linear_activated: unknown activation {activation!r}")
-    linear(x, w, out, op=op)
-    relu2(out)
+    # the activation is the product's epilogue, where the sum is finished: one range of K, or
+    # (decoding through a layer with few row tiles) the ranges of one cluster
+    if linear_tc_supported(x, w) and out.dtype == torch.bfloat16:
+        c = 0
+        if x.shape[0] <= 16:
+            tiles, kb, sms = (w.shape[0] + 127) // 128, (w.shape[1] + 63) // 64, n_sms()
+            c = 4 if tiles * 4 <= sms and kb >= 8 else 2 if tiles * 2 <= sms and kb >= 4 else 0
+        linear_tc(x, w, out, None, activation, splits=max(c, 1), cluster=c, op=op)
+    else:
+        linear_simt(x, w, out, None, activation, op=op)
 
 
 # ------------------------------------------------------------------- sampling

@@ -150,8 +150,10 @@ class LatentAttentionMixer:
                 lat = ctx.new(T, A, R)
                 kernels.attention_decode(ql.view(T, A * D), lat.view(T, A * R), view, ctx, A, 1, D,
                                          s.scale, 0, value_dim=R, values_in_keys=True)
-            kernels.heads_linear(lat, self.v_up, out.view(T, A, dv), op="v_up")
-        if G:
+            # (the output gate rides on the value up-projection)
+            kernels.heads_linear(lat, self.v_up, out.view(T, A, dv), op="v_up",
+                                 gate=row[:, Q + R + r:] if G else None)
+        if G and ctx.mode == PREFILL:
             kernels.gate_sigmoid(out, row[:, Q + R + r:])
         return self.out.partial(out)
 

@@ -31,7 +31,11 @@ Gemma 3 decoder of equal size (same width, heads, head size, layers and vocabula
 dense feed-forward as wide as the experts a token uses), random weights, one JSON line
 with, per size and model, prefill and decode throughput (recorded steps, CUDA events)
 and every operation's device time with its share of the measured peaks
-(``agave_b200.perf``, steps run launch by launch).
+(``agave_b200.perf``, steps run launch by launch).  ``--compare zazerax`` does the same for the
+Zazerax decoder (layers alternating latent attention of both kinds with windowed attention,
+dense squared-relu feed-forward) beside a Gemma 3 decoder of equal width, heads, layers and
+vocabulary whose every second layer has the same window and whose gated feed-forward has as
+many weights.
 """
 import argparse
 import json
@@ -253,6 +257,46 @@ def compare_configs(size):
     return ramilorn, gemma
 
 
+# Zazerax layer sizes for --compare: width, heads; latent attention: unrotated and rotated
+# head part, value head, kv latent, query latent (second kind); windowed attention: kv heads,
+# head size, window; feed-forward width; layers; vocabulary.
+ZAZERAX_SIZES = {
+    "small": dict(H=1024, A=16, d=32, r=32, dv=64, R=96, Rq=256, G=4, hd=64, window=512, ff=3072,
+                  L=8, V=32768),
+    "medium": dict(H=2048, A=16, d=64, r=64, dv=128, R=192, Rq=512, G=4, hd=128, window=1024,
+                   ff=6144, L=8, V=65536),
+    "large": dict(H=4096, A=32, d=128, r=64, dv=128, R=192, Rq=768, G=8, hd=128, window=1024,
+                  ff=12288, L=4, V=65536),
+}
+
+
+def compare_configs_zazerax(size):
+    z = ZAZERAX_SIZES[size]
+    rot = {"base": 10000.0, "dims": z["r"]}
+    lat = {"dim": z["d"], "heads": z["A"], "kv_rank": z["R"], "rot_dim": z["r"],
+           "scale": (z["d"] + z["r"]) ** -0.5, "vdim": z["dv"]}
+    first = dict(lat, rot=dict(rot, scaling={"factor": 4.0, "original": 4096, "fast": 32.0,
+                                             "slow": 1.0}))
+    second = dict(lat, rot=rot, q_rank=z["Rq"])
+    win = {"bias_max": 4 * z["window"], "bias_rows": 32, "dim": z["hd"], "heads": z["A"],
+           "kv_heads": z["G"], "mask": {"size": z["window"]}, "scale": z["hd"] ** -0.5,
+           "vdim": z["hd"]}
+    mlp = {"ff": z["ff"], "kind": "dense"}
+    kinds = [("latent_attention", first), ("attention", win), ("latent_attention_2", second),
+             ("attention", win)]
+    layers = [{"mixer": kinds[l % 4][1], "mlp": mlp, "type": kinds[l % 4][0]}
+              for l in range(z["L"])]
+    zazerax = {"architecture": "Zazerax", "embedding": {"scale": 1.0}, "layers": layers,
+               "norm": {"eps": 1e-5}, "vocab": z["V"], "width": z["H"]}
+    # (a gated feed-forward has three matrices where the dense one has two)
+    gemma = dict(CONFIG_1B, num_hidden_layers=z["L"], hidden_size=z["H"],
+                 num_attention_heads=z["A"], num_key_value_heads=z["G"], head_dim=z["hd"],
+                 query_pre_attn_scalar=z["hd"], intermediate_size=z["ff"] * 2 // 3 // 128 * 128,
+                 vocab_size=z["V"], sliding_window=z["window"], sliding_window_pattern=2,
+                 hidden_activation="silu")
+    return zazerax, gemma
+
+
 def run_compare(args):
     import torch
     from agave_b200 import kernels
@@ -263,12 +307,13 @@ def run_compare(args):
     from agave_b200.weights import random_tensors
     pk = peaks()
     batch, ctx_len, n_pre = 8, 1024, args.prefill_tokens
-    out = {"compare": "ramilorn beside gemma3 at equal size", "dtype": "bf16", "data": "synthetic",
-           "decode_batch": batch, "decode_context": ctx_len, "prefill_tokens": n_pre,
-           "peaks": pk, "sizes": {}}
+    builder = compare_configs_zazerax if args.compare == "zazerax" else compare_configs
+    out = {"compare": f"{args.compare} beside gemma3 at equal size", "dtype": "bf16",
+           "data": "synthetic", "decode_batch": batch, "decode_context": ctx_len,
+           "prefill_tokens": n_pre, "peaks": pk, "sizes": {}}
     for size in (args.compare_sizes or sorted(COMPARE_SIZES)):
         entry = {}
-        for name, cfg in zip(("ramilorn", "gemma3"), compare_configs(size)):
+        for name, cfg in zip((args.compare, "gemma3"), builder(size)):
             arch = resolve_architecture(cfg)
             specs = decoder_param_specs(arch.config_class.from_dict(cfg).to_model_spec())
             tensors = random_tensors(specs, 11, 0.02, 0.1, torch.bfloat16, "cuda:0")
@@ -384,7 +429,7 @@ def main():
                          "schedule's, 128 to 2,048 for the benchmark configuration)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="length of the timed prompt (default: the benchmark configuration's)")
-    ap.add_argument("--compare", default=None, choices=["ramilorn"],
+    ap.add_argument("--compare", default=None, choices=["ramilorn", "zazerax"],
                     help="instead of the benchmark: this architecture beside Gemma 3 at equal "
                          "layer sizes (see the module text)")
     ap.add_argument("--compare-sizes", nargs="+", default=None, choices=sorted(COMPARE_SIZES),

@@ -110,6 +110,38 @@ def test_gate_squared_relu_and_products_by_head(dtype):
         assert float(out[:, :, N + tail:].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T", [1, 5, 100, 300])
+@pytest.mark.parametrize("N, K", [(40, 72), (384, 256), (1024, 512)])
+def test_product_with_the_squared_relu_on_it(dtype, T, N, K):
+    """The dense feed-forward's first half: act(x w^T) in one kernel, in every form the
+    product takes (dot products, one-shot and cluster tiles, the prompt kernel)."""
+    from agave_b200 import kernels
+    td = TD[dtype]
+    x, w = rnd(T, K, seed=1).to(td), rnd(N, K, seed=2, std=K ** -0.5).to(td)
+    out = torch.empty(T, N, dtype=td, device=DEV)
+    kernels.linear_activated(x.to(DEV), w.to(DEV), out, "relu2")
+    ref = torch.relu(x.double() @ w.double().T) ** 2
+    assert rel_err(out, ref) < (1e-5 if dtype == "float32" else 1.5e-2)
+    assert kernels.linear_tc_status() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gate_on_the_products_by_head(dtype):
+    from agave_b200 import kernels
+    td = TD[dtype]
+    T, A, N, K = 6, 5, 12, 40
+    x, w = rnd(T, A, K, seed=4).to(td), rnd(A, N, K, seed=5, std=K ** -0.5).to(td)
+    ref = torch.einsum("ank,tak->tan", w.double(), x.double())
+    for width in (A, A * N):
+        g = rnd(T, width, seed=6, std=2.0).to(td)
+        out = torch.empty(T, A, N, dtype=td, device=DEV)
+        kernels.heads_linear(x.to(DEV), w.to(DEV), out, gate=g.to(DEV))
+        gate = torch.sigmoid(g.double())
+        want = ref * (gate[:, :, None] if width == A else gate.view(T, A, N))
+        assert rel_err(out, want) < (1e-5 if dtype == "float32" else 1.5e-2)
+
+
 def test_scaled_rotation_tables():
     from agave_b200.config.base import RotarySpec, WavelengthScalingSpec
     from agave_b200.parts.rope import RotaryEmbedding
