@@ -89,13 +89,13 @@ struct DecodeArgs {
     int max_pages, page, cap, nh, nkv, hd, window, n_splits, chunk;
     float scale;
     const float* sinks;        // [nh] sink logits (exp(sink) joins the denominator once), or null
-    const float* dist_bias;    // [n_dist, nh] added to the scaled score by distance, or null
+    const float* dist_bias;    // [nh, n_dist] added to the scaled score by distance, or null
     int n_dist;
 };
 
 // The learned bias of head h for the key at position j seen from position p.
 __device__ __forceinline__ float distance_bias(const DecodeArgs& a, int p, int j, int h) {
-    return a.dist_bias[(size_t)min(p - j, a.n_dist - 1) * a.nh + h];
+    return a.dist_bias[(size_t)h * a.n_dist + min(p - j, a.n_dist - 1)];
 }
 
 // What the sink of head h adds to a normaliser taken relative to the maximum m.
@@ -1380,7 +1380,7 @@ AGV_API int agv_attention_decode_ex(const void* q, long long q_stride, void* out
                                  max_keys, part_acc, part_ml, counters, stream, FuseQK{}, sinks);
 }
 
-// The same with a learned bias by distance: dist_bias [n_dist, nh] is added to the scaled
+// The same with a learned bias by distance: dist_bias [nh, n_dist] is added to the scaled
 // score of the key at distance min(p - j, n_dist - 1), or null.
 AGV_API int agv_attention_decode_ex2(const void* q, long long q_stride, void* out, int dtype,
                                      const void* k_pool, const void* v_pool, const int* page_table,

@@ -163,7 +163,7 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
                     val = s[i][e] * scale_log2e;
                     // a learned bias by distance, on the same base-2 scale as the score
                     if (dist_bias)
-                        val += dist_bias[(size_t)min(p - j, n_dist - 1) * nh + h] * 1.4426950408889634f;
+                        val += dist_bias[(size_t)h * n_dist + min(p - j, n_dist - 1)] * 1.4426950408889634f;
                 }
                 s[i][e] = val;
                 mx[e >> 1] = fmaxf(mx[e >> 1], val);
@@ -278,7 +278,7 @@ AGV_API int agv_attention_prefill_mma_supported(int hd, long long q_stride, long
 // greatest sequence length (sizes the grid).  window 0: no window.
 // sinks: [nh] sink logits (exp(sink) joins each row's softmax denominator once), or null.
 // hdv / v_stride: the value head size and the value rows' stride where they differ from the
-// keys' (out is then [T, nh * hdv]); dist_bias [n_dist, nh]: added to the scaled score of a key
+// keys' (out is then [T, nh * hdv]); dist_bias [nh, n_dist]: added to the scaled score of a key
 // at distance min(t - j, n_dist - 1), or null.
 AGV_API int agv_attention_prefill_mma_ex2(const void* q, long long q_stride, const void* k,
                                           const void* v, long long kv_stride, void* out,
@@ -312,6 +312,7 @@ AGV_API int agv_attention_prefill_mma_ex2(const void* q, long long q_stride, con
     const int widest = hd > hdv ? hd : hdv;
     if (widest <= 64) AGV_FA(64);
     if (widest <= 128) AGV_FA(128);
+    if (widest <= 192) AGV_FA(192);
     AGV_FA(256);
 #undef AGV_FA
 }

@@ -58,6 +58,9 @@ struct AtArgs {
     int kb;                        // 64-element blocks of head_dim
     int tmem_cols;
     const float* sinks;            // [nh] sink logits joining each row's denominator once, or null
+    const float* dist_bias;        // [nh, n_dist] learned bias by distance (unscaled), or null
+    int n_dist;
+    float inv_scale;               // 1 / scale: the bias joins the raw scores before the scale
 };
 
 // 2^x by the hardware approximation (relative error about 2^-22; -inf gives 0).
@@ -343,6 +346,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                     sv[c] = (key <= qp && key > lo) ? __uint_as_float(sr[c >> 4][c & 15]) : -INFINITY;
                 }
             }
+            if (a.dist_bias) {
+                // a learned bias by distance: the last table row stands for all farther keys
+                const float* dbp = a.dist_bias + (size_t)(head0 + hl) * a.n_dist;
+                const int d0 = qp - j0;                // distance of the tile's first key
+                if (d0 >= 63 && d0 < a.n_dist) {
+                    // every key of the tile lies behind the query and inside the table: the
+                    // row's 64 distances are 64 neighbours of the head's table row
+                    const float* dp = dbp + d0;
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) sv[c] = fmaf(dp[-c], a.inv_scale, sv[c]);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) {       // (unrolled whole: sv stays in registers)
+                        const int dist = d0 - c;
+                        if (dist >= 0) sv[c] = fmaf(dbp[min(dist, a.n_dist - 1)], a.inv_scale, sv[c]);
+                    }
+                }
+            }
             // the maximum of the raw scores, four chains side by side (the scale is positive)
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -545,12 +566,33 @@ AGV_API int agv_transpose_values(const void* v, long long kv_stride, void* vt, l
 // vt_ready != 0: vt already holds the transposed values (agv_qk_norm_rope_store
 // wrote them); else they are transposed here first.
 // sinks: [nh] sink logits or null; the scale must be positive.
+AGV_API int agv_attention_prefill_tc_ex2(const void* q, long long q_stride, const void* k,
+                                         const void* v, long long kv_stride, void* out, void* vt,
+                                         long long vt_cols, int vt_ready, const int* cu_seqlens, int B,
+                                         int T, int max_len, int nh, int nkv, int hd, float scale,
+                                         int window, const float* sinks, const float* dist_bias,
+                                         int n_dist, cudaStream_t stream);
+
 AGV_API int agv_attention_prefill_tc_ex(const void* q, long long q_stride, const void* k,
                                         const void* v, long long kv_stride, void* out, void* vt,
                                         long long vt_cols, int vt_ready, const int* cu_seqlens, int B,
                                         int T, int max_len, int nh, int nkv, int hd, float scale,
                                         int window, const float* sinks, cudaStream_t stream) {
+    return agv_attention_prefill_tc_ex2(q, q_stride, k, v, kv_stride, out, vt, vt_cols, vt_ready,
+                                        cu_seqlens, B, T, max_len, nh, nkv, hd, scale, window, sinks,
+                                        nullptr, 0, stream);
+}
+
+// The same with a learned bias by distance: dist_bias [nh, n_dist] is added to the scaled
+// score of the key at distance min(t - j, n_dist - 1), or null.
+AGV_API int agv_attention_prefill_tc_ex2(const void* q, long long q_stride, const void* k,
+                                         const void* v, long long kv_stride, void* out, void* vt,
+                                         long long vt_cols, int vt_ready, const int* cu_seqlens, int B,
+                                         int T, int max_len, int nh, int nkv, int hd, float scale,
+                                         int window, const float* sinks, const float* dist_bias,
+                                         int n_dist, cudaStream_t stream) {
     AGV_REQUIRE(scale > 0.f, "attention: the tcgen05 kernel takes a positive score scale");
+    AGV_REQUIRE(!dist_bias || n_dist > 0, "attention: an empty distance table");
     AGV_REQUIRE(B >= 0 && T >= 0 && nh > 0 && nkv > 0 && hd > 0 && max_len >= 0,
                 "attention: bad sizes");
     AGV_REQUIRE(nh % nkv == 0, "attention: %d heads are not a multiple of %d kv heads", nh, nkv);
@@ -578,6 +620,9 @@ AGV_API int agv_attention_prefill_tc_ex(const void* q, long long q_stride, const
     a.kb = (hd + 63) / 64;
     a.tmem_cols = AT_O_COL + hd <= 256 ? 256 : 512;
     a.sinks = sinks;
+    a.dist_bias = dist_bias;
+    a.n_dist = n_dist;
+    a.inv_scale = 1.0f / scale;
 
     CUtensorMap mq, mk, mvt;
     {

@@ -30,9 +30,9 @@ struct PagedKV {
     int v_row;                 // elements between two positions' value rows (0: nkv * hdv)
 };
 
-// A learned bias per (distance, head) added to the scaled score: bias[min(p - j, n - 1), h].
+// A learned bias per (head, distance) added to the scaled score: bias[h, min(p - j, n - 1)].
 struct DistanceBias {
-    const float* bias;         // [n, nh] or null
+    const float* bias;         // [nh, n] or null
     int n;
 };
 
@@ -92,7 +92,7 @@ attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T* __re
             if (e < hd) s = fmaf(qr[i], to_f32(kp[e]), s);
         }
         s = warp_sum(s) * scale;
-        if (db.bias) s += db.bias[(size_t)min(p - j, db.n - 1) * nh + h];
+        if (db.bias) s += db.bias[(size_t)h * db.n + min(p - j, db.n - 1)];
         const float mn = fmaxf(m, s);
         const float alpha = expf(m - mn);      // exp(-inf) = 0 on the first key
         const float w = expf(s - mn);

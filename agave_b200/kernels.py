@@ -545,21 +545,21 @@ def attention_prefill_simt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ou
                            dist_bias: Optional[torch.Tensor] = None) -> None:
     """Prompts that start at 0; q [T, nh*hd], k [T, nkv*hd], v [T, nkv*hdv] row-strided
     views (hdv = value_dim or head_dim), out [T, nh*hdv]; ``sinks`` [nh]: a logit per query
-    head that joins its softmax denominator once; ``dist_bias`` [n, nh]: added to the scaled
+    head that joins its softmax denominator once; ``dist_bias`` [nh, n]: added to the scaled
     score of a key at distance min(t - j, n - 1)."""
     T = q.shape[0]
     assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1
     _dense(out, "out"); _f32(sinks, "sinks"); _f32(dist_bias, "dist_bias")
     if dist_bias is not None:
         _dense(dist_bias, "dist_bias")
-        assert dist_bias.dim() == 2 and dist_bias.shape[1] == n_heads
+        assert dist_bias.dim() == 2 and dist_bias.shape[0] == n_heads
     _i32(positions, "positions"); _i32(seq_index, "seq_index"); _i32(cu_seqlens, "cu_seqlens")
     _check(library().agv_attention_prefill_simt_ex(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), _ptr(v),
         ctypes.c_longlong(k.stride(0)), _ptr(out), dtype_code(q.dtype), _ptr(positions),
         _ptr(seq_index), _ptr(cu_seqlens), T, n_heads, n_kv_heads, head_dim,
         ctypes.c_float(scale), window, value_dim or head_dim, ctypes.c_longlong(v.stride(0)),
-        _ptr(sinks), _ptr(dist_bias), dist_bias.shape[0] if dist_bias is not None else 0,
+        _ptr(sinks), _ptr(dist_bias), dist_bias.shape[1] if dist_bias is not None else 0,
         _stream()))
 
 
@@ -578,7 +578,7 @@ def attention_paged_simt(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tenso
     _f32(sinks, "sinks"); _f32(dist_bias, "dist_bias")
     if dist_bias is not None:
         _dense(dist_bias, "dist_bias")
-        assert dist_bias.dim() == 2 and dist_bias.shape[1] == n_heads
+        assert dist_bias.dim() == 2 and dist_bias.shape[0] == n_heads
     _dense(out, "out"); _dense(k_pool, "k_pool"); _dense(v_pool, "v_pool")
     for t, n in ((positions, "positions"), (page_table, "page_table"), (slots, "slots"),
                  (seq_index, "seq_index")):
@@ -589,7 +589,7 @@ def attention_paged_simt(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tenso
         _ptr(v_pool), _ptr(page_table), _ptr(slots), _ptr(positions), _ptr(seq_index),
         page_table.shape[1], page, cap, T, n_heads, n_kv_heads, head_dim,
         ctypes.c_float(scale), window, value_dim or head_dim, _ptr(sinks), _ptr(dist_bias),
-        dist_bias.shape[0] if dist_bias is not None else 0, int(v_row), _stream()))
+        dist_bias.shape[1] if dist_bias is not None else 0, int(v_row), _stream()))
 
 
 # ------------------------------------------- rows of stacked projections, latent attention
@@ -1074,7 +1074,7 @@ def attention_prefill_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out
                           dist_bias: Optional[torch.Tensor] = None) -> None:
     """Prompts that start at 0 on the tensor cores (bfloat16, head sizes in steps
     of 8 up to 256); q, k, v are row-strided views, out is dense.  ``value_dim``: the value
-    head size where it differs from the keys'; ``dist_bias`` [n, nh]: see
+    head size where it differs from the keys'; ``dist_bias`` [nh, n]: see
     ``attention_prefill_simt``."""
     _f32(sinks, "sinks"); _f32(dist_bias, "dist_bias")
     assert q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype
@@ -1082,13 +1082,13 @@ def attention_prefill_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out
     _dense(out, "out"); _i32(cu_seqlens, "cu_seqlens")
     if dist_bias is not None:
         _dense(dist_bias, "dist_bias")
-        assert dist_bias.dim() == 2 and dist_bias.shape[1] == n_heads
+        assert dist_bias.dim() == 2 and dist_bias.shape[0] == n_heads
     _check(library().agv_attention_prefill_mma_ex2(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), _ptr(v),
         ctypes.c_longlong(k.stride(0)), _ptr(out), _ptr(cu_seqlens), cu_seqlens.numel() - 1,
         max_len, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window, _ptr(sinks),
         value_dim or head_dim, ctypes.c_longlong(v.stride(0)), _ptr(dist_bias),
-        dist_bias.shape[0] if dist_bias is not None else 0, _stream()))
+        dist_bias.shape[1] if dist_bias is not None else 0, _stream()))
 
 
 def prefill_values_scratch(T: int, B: int, n_kv_heads: int, head_dim: int,
@@ -1114,7 +1114,8 @@ def attention_prefill_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out:
                          cu_seqlens: torch.Tensor, max_len: int, n_heads: int, n_kv_heads: int,
                          head_dim: int, scale: float, window: int,
                          vt: Optional[torch.Tensor] = None,
-                         sinks: Optional[torch.Tensor] = None) -> None:
+                         sinks: Optional[torch.Tensor] = None,
+                         dist_bias: Optional[torch.Tensor] = None) -> None:
     """Prompts that start at 0 on the tcgen05 tensor cores (bfloat16, head sizes in
     steps of 16 up to 256); q, k, v are row-strided views, out is dense.  ``vt``:
     the values already transposed (by ``qk_norm_rope_store``); else this call
@@ -1128,12 +1129,16 @@ def attention_prefill_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out:
     if vt is None:
         vt = prefill_values_scratch(T, B, n_kv_heads, head_dim, q.device)
     _dense(vt, "vt")
-    _f32(sinks, "sinks")
-    _check(library().agv_attention_prefill_tc_ex(
+    _f32(sinks, "sinks"); _f32(dist_bias, "dist_bias")
+    if dist_bias is not None:
+        _dense(dist_bias, "dist_bias")
+        assert dist_bias.dim() == 2 and dist_bias.shape[0] == n_heads
+    _check(library().agv_attention_prefill_tc_ex2(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), _ptr(v),
         ctypes.c_longlong(k.stride(0)), _ptr(out), _ptr(vt), ctypes.c_longlong(vt.shape[1]),
         1 if ready else 0, _ptr(cu_seqlens), B, T, max_len, n_heads, n_kv_heads, head_dim,
-        ctypes.c_float(scale), window, _ptr(sinks), _stream()))
+        ctypes.c_float(scale), window, _ptr(sinks), _ptr(dist_bias),
+        dist_bias.shape[1] if dist_bias is not None else 0, _stream()))
 
 
 def attention_tc_status() -> int:
@@ -1160,7 +1165,8 @@ def attention_prefill_wants_transposed_values(qkv: torch.Tensor, head_dim: int,
 
 
 def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, window,
-                      vt=None, value_dim: int = 0, sinks=None, dist_bias=None) -> None:
+                      vt=None, value_dim: int = 0, sinks=None, dist_bias=None,
+                      op: str = "attention") -> None:
     """Prompt attention of one layer in bfloat16: the tcgen05 kernel for head sizes
     in steps of 16 up to 256, the mma.sync kernel for the other multiples of 8; else
     (and for value heads of another size than the keys') the one-warp-per-(token, head)
@@ -1169,13 +1175,13 @@ def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, w
     aligned = (q.dtype == torch.bfloat16 and head_dim <= 256 and hdv <= 256 and
                q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 and v.stride(0) % 8 == 0 and
                q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0)
-    # the tcgen05 kernel knows neither value heads of their own size nor a distance bias
-    same = hdv == head_dim and dist_bias is None and k.stride(0) == v.stride(0)
-    with _span("attention", *_attention_cost(ctx, q, k, v, out, n_heads, head_dim, window)):
+    # the tcgen05 kernel does not know value heads of their own size
+    same = hdv == head_dim and k.stride(0) == v.stride(0)
+    with _span(op, *_attention_cost(ctx, q, k, v, out, n_heads, head_dim, window)):
         if (aligned and same and head_dim % 16 == 0 and _PREFILL_TC and scale > 0 and
                 q.shape[0] > PREFILL_TC_MIN_TOKENS):
             attention_prefill_tc(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads, n_kv_heads,
-                                 head_dim, scale, window, vt=vt, sinks=sinks)
+                                 head_dim, scale, window, vt=vt, sinks=sinks, dist_bias=dist_bias)
         elif aligned and head_dim % 8 == 0 and hdv % 8 == 0:
             attention_prefill_mma(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads,
                                   n_kv_heads, head_dim, scale, window, sinks=sinks,
@@ -1285,13 +1291,13 @@ def attention_decode_split(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Ten
     _f32(sinks, "sinks"); _f32(dist_bias, "dist_bias")
     if dist_bias is not None:
         _dense(dist_bias, "dist_bias")
-        assert dist_bias.dim() == 2 and dist_bias.shape[1] == n_heads
+        assert dist_bias.dim() == 2 and dist_bias.shape[0] == n_heads
     _check(library().agv_attention_decode_ex2(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(out), dtype_code(q.dtype), _ptr(k_pool),
         _ptr(v_pool), _ptr(page_table), _ptr(slots), _ptr(positions), page_table.shape[1], page,
         cap, B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window, max_keys,
         _ptr(part_acc), _ptr(part_ml), _ptr(counters), _ptr(sinks), _ptr(dist_bias),
-        dist_bias.shape[0] if dist_bias is not None else 0, _stream()))
+        dist_bias.shape[1] if dist_bias is not None else 0, _stream()))
 
 
 _FUSED_DECODE = os.environ.get("AGAVE_B200_FUSED_DECODE_ATTENTION", "1") != "0"
@@ -1348,13 +1354,13 @@ def attention_decode_fused(partial: torch.Tensor, wq: Optional[torch.Tensor],
 
 def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, window,
                      value_dim: int = 0, sinks=None, dist_bias=None,
-                     values_in_keys: bool = False) -> None:
+                     values_in_keys: bool = False, op: str = "attention") -> None:
     """Decode attention of one layer: the split kernel for head sizes in steps of
     16 up to 512, else (and for value heads of another size than the keys') the
     one-warp-per-head kernel."""
     hdv = value_dim or head_dim
-    with _span("attention", *_attention_cost(ctx, q, None, None, out, n_heads, head_dim, window,
-                                             n_kv_heads)):
+    with _span(op, *_attention_cost(ctx, q, None, None, out, n_heads, head_dim, window,
+                                    n_kv_heads)):
         if head_dim % 16 == 0 and head_dim <= 512 and hdv == head_dim and not values_in_keys:
             max_keys = min(window, ctx.max_len) if window else ctx.max_len
             attention_decode_split(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,

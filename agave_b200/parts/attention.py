@@ -160,7 +160,7 @@ class AttentionMixer:
                 n = min(n, int(self.spec.window))
             idx = torch.tensor(self.distance_rows(db.rows, db.far, max(n, 1)), device=device)
             table = tensors["distance_bias"].to(device=device, dtype=torch.float32)
-            self.dist_bias = table[idx].contiguous()
+            self.dist_bias = table[idx].t().contiguous()          # [heads, distances]
 
     def forward(self, x: torch.Tensor, ctx, cache_entry: int, writes_cache: bool) -> torch.Tensor:
         if not self.plain:

@@ -132,7 +132,7 @@ class LatentAttentionMixer:
             k = ctx.new(T, A * hw)
             kernels.assemble_keys(kv[:, :A * d], kr, k, A, d, r)
             kernels.attention_prefill(q, k, kv[:, A * d:], out, ctx, A, A, hw, s.scale, 0,
-                                      value_dim=dv)
+                                      value_dim=dv, op="latent_attention")
         else:
             # the key up-projection goes into the query (the rotated part passes through);
             # the heads attend to the cache rows themselves
@@ -144,12 +144,13 @@ class LatentAttentionMixer:
                 # head in its group; the r values behind the latent's weighted sum are unused
                 lat = ctx.new(T, A, D)
                 kernels.attention_decode(ql.view(T, A * D), lat.view(T, A * D), view, ctx, A, 1, D,
-                                         s.scale, 0)
+                                         s.scale, 0, op="latent_attention")
                 lat = lat[:, :, :R]
             else:
                 lat = ctx.new(T, A, R)
                 kernels.attention_decode(ql.view(T, A * D), lat.view(T, A * R), view, ctx, A, 1, D,
-                                         s.scale, 0, value_dim=R, values_in_keys=True)
+                                         s.scale, 0, value_dim=R, values_in_keys=True,
+                                         op="latent_attention")
             # (the output gate rides on the value up-projection)
             kernels.heads_linear(lat, self.v_up, out.view(T, A, dv), op="v_up",
                                  gate=row[:, Q + R + r:] if G else None)

@@ -360,7 +360,7 @@ def test_prompt_attention_with_window_bias_and_one_in_the_denominator(dtype, T, 
     ref = P.softmax_attention(q.double(), k.double(), v.double(), scale, window=window,
                               bias=bias, far=far, one_in_denominator=True)
     idx = torch.tensor(AttentionMixer.distance_rows(rows, far, min(window, math.ceil(far) + 1)))
-    table = bias[idx].float().contiguous().to(DEV)
+    table = bias[idx].float().t().contiguous().to(DEV)
     lens = [T, 3]
     oc = _Cache(KVRequest(G, d, window, dv), lens, td)
     ctx = oc.context(PREFILL, lens)
@@ -407,7 +407,7 @@ def test_decode_attention_with_window_bias_and_one_in_the_denominator(dtype, T, 
         qs.append(q[n - 1])
         refs.append(ref[-1])
     ctx = oc.context(DECODE, [1] * len(lens))
-    table = bias[idx].float().contiguous().to(DEV)
+    table = bias[idx].float().t().contiguous().to(DEV)
     B = len(lens)
     out = torch.empty(B, A * dv, dtype=td, device=DEV)
     kernels.attention_decode(torch.stack(qs).reshape(B, A * d).to(DEV), out, oc.cache.kv_view(0),
@@ -417,6 +417,27 @@ def test_decode_attention_with_window_bias_and_one_in_the_denominator(dtype, T, 
     tol = 3e-5 if dtype == "float32" else 2e-2
     for b in range(B):
         assert rel_err(out[b].view(A, dv), refs[b]) < tol, (b, lens[b])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T, A, d, dv", [(150, 2, 160, 96), (230, 2, 192, 128), (70, 3, 64, 80),
+                                         (40, 2, 18, 10), (260, 2, 128, 128)])
+def test_prompt_attention_with_value_heads_of_their_own_size(dtype, T, A, d, dv):
+    """As many key/value heads as query heads, keys and values of different widths (what a
+    latent attention's prompt step rebuilds), in every width the tensor-core forms pad to."""
+    from agave_b200 import kernels
+    from agave_b200.engine.batch import PREFILL
+    from agave_b200.parts.base import KVRequest
+    td = TD[dtype]
+    scale = 1.3 / d ** 0.5
+    q, k, v = (rnd(T, A, d, seed=1).to(td), rnd(T, A, d, seed=2).to(td), rnd(T, A, dv, seed=3).to(td))
+    ref = P.softmax_attention(q.double(), k.double(), v.double(), scale)
+    oc = _Cache(KVRequest(A, d, None, dv), [T], td)
+    ctx = oc.context(PREFILL, [T])
+    out = torch.empty(T, A * dv, dtype=td, device=DEV)
+    kernels.attention_prefill(q.reshape(T, -1).to(DEV), k.reshape(T, -1).to(DEV),
+                              v.reshape(T, -1).to(DEV), out, ctx, A, A, d, scale, 0, value_dim=dv)
+    assert rel_err(out.view(T, A, dv), ref) < (3e-5 if dtype == "float32" else 2e-2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -442,7 +463,7 @@ def test_a_far_key_among_hundreds_decides_without_a_window(dtype):
         ref[a] = w @ v.double()[:, a // (A // G)]
     assert (ref[0] - v.double()[3, 0]).abs().max() < 0.05 * v.double()[3, 0].abs().max() + 0.05
     idx = torch.tensor(AttentionMixer.distance_rows(rows, far, math.ceil(far) + 1))
-    table = bias[idx].float().contiguous().to(DEV)
+    table = bias[idx].float().t().contiguous().to(DEV)
     oc = _Cache(KVRequest(G, d, None, 0), [T], td)
     oc.fill(0, k.to(DEV), v.to(DEV))
     tol = 3e-5 if dtype == "float32" else 2e-2
