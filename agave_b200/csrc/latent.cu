@@ -43,6 +43,41 @@ struct RowIn {
         }
         return to_f32(row[(size_t)t * ld + e]);
     }
+    // The whole row of token t into shared memory, 32-bit: eight values per thread at a
+    // time with all their loads issued before the first is used (a dependent trip to L2 or
+    // HBM costs about a microsecond, and a decode step has few rows to hide it behind).
+    __device__ __forceinline__ void load(int t, float* buf) const {
+        for (int e0 = threadIdx.x; e0 < W; e0 += blockDim.x * 8) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.f;
+            if (part) {
+                const float* p = part + (size_t)t * W;
+#pragma unroll 2
+                for (int sp = 0; sp < n_splits; ++sp) {
+                    const float* ps = p + (size_t)sp * split_stride;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int e = e0 + i * blockDim.x;
+                        if (e < W) v[i] += ps[e];
+                    }
+                }
+            } else {
+                const T* r = row + (size_t)t * ld;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int e = e0 + i * blockDim.x;
+                    if (e < W) v[i] = to_f32(r[e]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int e = e0 + i * blockDim.x;
+                if (e < W) buf[e] = v[i];
+            }
+        }
+        __syncthreads();
+    }
 };
 
 // Cache row of token t, or null when nothing is stored for it (padding, or a ring row that
@@ -79,11 +114,11 @@ proj_norm_store_kernel(RowIn<T> in, T* __restrict__ out, long long ldo, int n_to
     const int t = blockIdx.x;
     const int W = nq + nk + nv;
     float sq = 0.f, sk = 0.f;
-    for (int e = threadIdx.x; e < W; e += blockDim.x) {
-        const float v = in.at(t, e);
-        buf[e] = v;
+    in.load(t, buf);
+    for (int e = threadIdx.x; e < nq + nk; e += blockDim.x) {
+        const float v = buf[e];
         if (e < nq) sq += v * v;
-        else if (e < nq + nk) sk += v * v;
+        else sk += v * v;
     }
     const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)nq + eps);
     const float rk = 1.0f / sqrtf(block_sum(sk, red) / (float)nk + eps);
@@ -115,14 +150,13 @@ latent_prepare_kernel(RowIn<T> in, T* __restrict__ out, long long ldo, int n_tok
     extern __shared__ float buf[];
     __shared__ float red[33];
     const int t = blockIdx.x;
-    const int W = q_width + R + r + G;
     const int c_at = q_width, kr_at = q_width + R, g_at = q_width + R + r;
     float sq = 0.f, sc = 0.f;
-    for (int e = threadIdx.x; e < W; e += blockDim.x) {
-        const float v = in.at(t, e);
-        buf[e] = v;
+    in.load(t, buf);
+    for (int e = threadIdx.x; e < kr_at; e += blockDim.x) {
+        const float v = buf[e];
         if (e < q_width) sq += v * v;
-        else if (e < kr_at) sc += v * v;
+        else sc += v * v;
     }
     float rq = 1.f;
     if (q_latent) rq = 1.0f / sqrtf(block_sum(sq, red) / (float)q_width + eps);
@@ -291,6 +325,67 @@ __global__ void gate_sigmoid_kernel(T* __restrict__ out, long long ldo, const T*
     }
 }
 
+// The same in 16-byte pieces of eight bfloat16 values: a logit per value (per == 1) or per
+// `per` values with per a multiple of 8; width and both strides multiples of 8.
+__global__ void gate_sigmoid_bf16x8_kernel(__nv_bfloat16* __restrict__ out, long long ldo,
+                                           const __nv_bfloat16* __restrict__ g, long long ldg,
+                                           int n_tokens, int width, int per) {
+    pdl_wait();
+    pdl_launch_next();
+    const int cpr = width / 8;
+    const long long n = (long long)n_tokens * cpr;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long t = idx / cpr;
+        const int c = (int)(idx - t * cpr) * 8;
+        uint4 ov = *reinterpret_cast<const uint4*>(out + t * ldo + c);
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+        float z[8];
+        if (per == 1) {
+            const uint4 gv = *reinterpret_cast<const uint4*>(g + t * ldg + c);
+            const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(g2[i]);
+                z[2 * i] = f.x;
+                z[2 * i + 1] = f.y;
+            }
+        } else {
+            const float zz = __bfloat162float(g[t * ldg + c / per]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) z[i] = zz;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = __bfloat1622float2(o2[i]);
+            f.x = f.x / (1.0f + __expf(-z[2 * i]));
+            f.y = f.y / (1.0f + __expf(-z[2 * i + 1]));
+            o2[i] = __floats2bfloat162_rn(f.x, f.y);
+        }
+        *reinterpret_cast<uint4*>(out + t * ldo + c) = ov;
+    }
+}
+
+// Key assembly in 16-byte pieces: d, r and both strides multiples of 8 (bfloat16).
+__global__ void assemble_keys_bf16x8_kernel(const __nv_bfloat16* __restrict__ k_plain,
+                                            long long ldp, const __nv_bfloat16* __restrict__ kr,
+                                            long long ldr, __nv_bfloat16* __restrict__ k_out,
+                                            int n_tokens, int heads, int d, int r) {
+    pdl_wait();
+    pdl_launch_next();
+    const int cph = (d + r) / 8, cpr = heads * cph;
+    const long long n = (long long)n_tokens * cpr;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long t = idx / cpr;
+        const int rem = (int)(idx - t * cpr);
+        const int a = rem / cph, i = (rem - a * cph) * 8;
+        const __nv_bfloat16* src = i < d ? k_plain + t * ldp + (size_t)a * d + i
+                                         : kr + t * ldr + (i - d);
+        *reinterpret_cast<uint4*>(k_out + idx * 8) = *reinterpret_cast<const uint4*>(src);
+    }
+}
+
 template <typename T>
 __global__ void relu2_kernel(T* __restrict__ z, long long n) {
     pdl_wait();
@@ -444,6 +539,11 @@ AGV_API int agv_assemble_keys(const void* k_plain, long long ldp, const void* kr
     if (dtype == AGV_F32)
         agv_launch(assemble_keys_kernel<float>, flat_grid(n, 256), 256, 0, stream,
                    (const float*)k_plain, ldp, (const float*)kr, ldr, (float*)k_out, T, heads, d, r);
+    else if (dtype == AGV_BF16 && d % 8 == 0 && r % 8 == 0 && ldp % 8 == 0 && ldr % 8 == 0 &&
+             agv_aligned(k_plain, 16) && agv_aligned(kr, 16) && agv_aligned(k_out, 16))
+        agv_launch(assemble_keys_bf16x8_kernel, flat_grid(n / 8, 256), 256, 0, stream,
+                   (const __nv_bfloat16*)k_plain, ldp, (const __nv_bfloat16*)kr, ldr,
+                   (__nv_bfloat16*)k_out, T, heads, d, r);
     else if (dtype == AGV_BF16)
         agv_launch(assemble_keys_kernel<__nv_bfloat16>, flat_grid(n, 256), 256, 0, stream,
                    (const __nv_bfloat16*)k_plain, ldp, (const __nv_bfloat16*)kr, ldr,
@@ -501,6 +601,10 @@ AGV_API int agv_gate_sigmoid(void* out, long long ldo, const void* g, long long 
     if (dtype == AGV_F32)
         agv_launch(gate_sigmoid_kernel<float>, flat_grid(n, 256), 256, 0, stream, (float*)out, ldo,
                    (const float*)g, ldg, T, width, per);
+    else if (dtype == AGV_BF16 && width % 8 == 0 && (per == 1 || per % 8 == 0) && ldo % 8 == 0 &&
+             (per != 1 || ldg % 8 == 0) && agv_aligned(out, 16) && (per != 1 || agv_aligned(g, 16)))
+        agv_launch(gate_sigmoid_bf16x8_kernel, flat_grid(n / 8, 256), 256, 0, stream,
+                   (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)g, ldg, T, width, per);
     else if (dtype == AGV_BF16)
         agv_launch(gate_sigmoid_kernel<__nv_bfloat16>, flat_grid(n, 256), 256, 0, stream,
                    (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)g, ldg, T, width, per);

@@ -12,7 +12,7 @@ go through W_o.  The queries come from x directly (W_q) or, with ``q_rank``, thr
 latent of their own (W_uq rmsnorm(W_dq x)).
 
 Two ways to compute the same sums.  A prompt step rebuilds keys and values for its tokens
-(one product W_uk | W_uv on c) and runs ordinary multi-head attention over the step's own
+(the products W_uk c and W_uv c) and runs ordinary multi-head attention over the step's own
 tensors.  A decode step never rebuilds them: W_uk is absorbed into the query
 (q'_a = W_uk,a^T q_a[:d], ``kv_rank`` wide), every head attends to the cache rows
 themselves, whose leading ``kv_rank`` values also serve as values, and W_uv is applied to
@@ -50,7 +50,8 @@ class LatentAttentionMixer:
                            "head": spec.n_heads}[spec.gate]
         self.down: Optional[Linear] = None        # Q | c | kr | g from x
         self.q_up: Optional[Linear] = None
-        self.kv_up: Optional[Linear] = None       # k_plain | v from c (prompts)
+        self.k_up: Optional[Linear] = None        # k_plain from c (prompts)
+        self.v_up_prompt: Optional[Linear] = None # v from c (prompts)
         self.k_absorb: Optional[torch.Tensor] = None   # [A, kv_rank, d]: W_uk per head, transposed
         self.v_up: Optional[torch.Tensor] = None       # [A, value_dim, kv_rank]
         self.out: Optional[Linear] = None
@@ -98,7 +99,10 @@ class LatentAttentionMixer:
         self.w_c_norm = tensors["kv_down_norm.weight"].to(device=device,
                                                           dtype=torch.float32).contiguous()
         uk, uv = mat("k_up.weight"), mat("v_up.weight")
-        self.kv_up = Linear(torch.cat([uk, uv], dim=0).contiguous(), role="kv_up")
+        # (two products, so that the values come out dense: the prompt attention kernels
+        # want keys and values at one row stride)
+        self.k_up = Linear(uk.contiguous(), role="kv_up")
+        self.v_up_prompt = Linear(uv.contiguous(), role="kv_up")
         self.k_absorb = uk.view(A, d, R).transpose(1, 2).contiguous()
         self.v_up = uv.view(A, dv, R).contiguous()
         self.out = Linear(mat("o_proj.weight").contiguous(), role="out_proj")
@@ -128,10 +132,9 @@ class LatentAttentionMixer:
         c, kr = row[:, Q:Q + R], row[:, Q + R:Q + R + r]
         out = ctx.new(T, A * dv)
         if ctx.mode == PREFILL:
-            kv = self.kv_up(c)
             k = ctx.new(T, A * hw)
-            kernels.assemble_keys(kv[:, :A * d], kr, k, A, d, r)
-            kernels.attention_prefill(q, k, kv[:, A * d:], out, ctx, A, A, hw, s.scale, 0,
+            kernels.assemble_keys(self.k_up(c), kr, k, A, d, r)
+            kernels.attention_prefill(q, k, self.v_up_prompt(c), out, ctx, A, A, hw, s.scale, 0,
                                       value_dim=dv, op="latent_attention")
         else:
             # the key up-projection goes into the query (the rotated part passes through);

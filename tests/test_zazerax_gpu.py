@@ -721,3 +721,76 @@ def test_trace_replay_as_a_process(dtype):
             want.append(refs["b"][30 + k:31 + k])
     rows_agree(torch.cat(rows), torch.cat(want), dtype, "decoded")
     shutil.rmtree(out, ignore_errors=True)
+
+
+def test_command_line_on_this_architecture():
+    """``python -m agave_b200`` picks the model class from config.json: greedy tokens equal the
+    plain model's, --model-info names the architecture, --profile lists this design's
+    operations, --random-weights draws a model from a config.json that states the distance
+    tables' rows."""
+    import copy
+    from zazerax_util import BIAS_ROWS
+    name = "Z2"
+    folder = folder_for(name, torch.float32)
+    V = vocab(name)
+    prompt = tokens(9, V, 31)
+
+    def run(*args):
+        env = dict(os.environ)
+        env["PYTHONPATH"] = ROOT + os.pathsep + env.get("PYTHONPATH", "")
+        return subprocess.run([sys.executable, "-m", "agave_b200", *args], capture_output=True,
+                              text=True, timeout=900, env=env, cwd=ROOT)
+    toks = ",".join(str(t) for t in prompt)
+    r = run(folder, "--tokens", toks, "-n", "6", "--json", "--dtype", "float32")
+    assert r.returncode == 0, r.stderr[-2000:]
+    out = json.loads(r.stdout.strip().splitlines()[-1])["output_ids"]
+    assert len(out) == 6
+    ref = plain_logits(folder, prompt + out)
+    for k, t in enumerate(out):
+        row = ref[len(prompt) - 1 + k]
+        assert float(row.max() - row[t]) <= 2e-3 * float(row.abs().max()), (k, t)
+    r = run(folder, "--model-info", "--json")
+    assert r.returncode == 0 and "Zazerax" in r.stdout, r.stderr[-2000:]
+    r = run(folder, "--tokens", toks, "-n", "3", "--profile", "--dtype", "bfloat16")
+    assert r.returncode == 0, r.stderr[-2000:]
+    for op in ("norm", "qkv", "attention", "latent_attention", "q_absorb", "v_up", "out_proj", "up",
+               "down", "lm_head", "TOTAL"):
+        assert op in r.stderr, (op, r.stderr[-1500:])
+    raw = copy.deepcopy(CONFIGS[name])
+    for i, layer in enumerate(raw["layers"]):
+        if layer["type"] == "attention":
+            layer["mixer"]["bias_rows"] = BIAS_ROWS[name][layer.get("weights_of", i)]
+    with tempfile.TemporaryDirectory() as d:
+        with open(os.path.join(d, "config.json"), "w") as f:
+            json.dump(raw, f)
+        outs = []
+        for seed in ("3", "3", "4"):
+            r = run(d, "--random-weights", seed, "--tokens", toks, "-n", "5", "--json")
+            assert r.returncode == 0, r.stderr[-2000:]
+            outs.append(json.loads(r.stdout.strip().splitlines()[-1])["output_ids"])
+        assert outs[0] == outs[1] and len(outs[0]) == 5
+
+
+def test_trace_replay_counts_tokens_not_pages():
+    """--max-tokens counts the tokens live requests hold, without the padding of the cache's
+    pages: a dozen requests of two or three tokens each fit a budget of 36."""
+    name = "Z1"
+    folder = folder_for(name, torch.float32)
+    V = vocab(name)
+    seqs = {f"q{i}": tokens(3, V, 700 + i) for i in range(12)}
+    steps = [{"step": 0, "entries": [{"id": k, "tokens": s[:2], "want": [1]}
+                                     for k, s in seqs.items()], "end": []},
+             {"step": 1, "entries": [{"id": k, "tokens": s[2:], "want": [0]}
+                                     for k, s in seqs.items()], "end": list(seqs)}]
+    out = tempfile.mkdtemp(prefix="zazerax_trace_")
+    text = "".join(json.dumps(s) + "\n" for s in steps)
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder,
+                        "--dtype", "float32", "--out", out, "--max-tokens", "36"],
+                       input=text, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    refs = [plain_logits(folder, s) for s in seqs.values()]
+    for step, row in ((0, 1), (1, 2)):
+        got = torch.from_numpy(np.fromfile(os.path.join(out, f"{step}.f32"), dtype="<f4")
+                               .reshape(12, V))
+        rows_agree(got, torch.stack([ref[row] for ref in refs]), "float32", f"step {step}")
+    shutil.rmtree(out, ignore_errors=True)
