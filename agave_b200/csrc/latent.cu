@@ -53,7 +53,7 @@ struct RowIn {
             for (int i = 0; i < 8; ++i) v[i] = 0.f;
             if (part) {
                 const float* p = part + (size_t)t * W;
-#pragma unroll 2
+#pragma unroll 4
                 for (int sp = 0; sp < n_splits; ++sp) {
                     const float* ps = p + (size_t)sp * split_stride;
 #pragma unroll
@@ -103,7 +103,7 @@ __device__ __forceinline__ void rotate_pair(float u, float v, float c, float s, 
 
 // ------------------------------------------------------- whole-projection norm
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 proj_norm_store_kernel(RowIn<T> in, T* __restrict__ out, long long ldo, int n_tokens, int nq,
                        int nk, int nv, const float* __restrict__ wq, const float* __restrict__ wk,
                        float eps, const int* __restrict__ positions, CacheWrite cw) {
@@ -139,7 +139,7 @@ proj_norm_store_kernel(RowIn<T> in, T* __restrict__ out, long long ldo, int n_to
 
 // ------------------------------------------------------------ latent prepare
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 latent_prepare_kernel(RowIn<T> in, T* __restrict__ out, long long ldo, int n_tokens, int q_width,
                       int q_latent, int heads, int d, int r, int R, int G,
                       const float* __restrict__ w_q, const float* __restrict__ w_c, float eps,
@@ -411,6 +411,10 @@ __global__ void rope_table_freqs_kernel(const int* __restrict__ positions,
     sinv[idx] = (float)(s * mult);
 }
 
+// Threads of a one-CTA-per-token kernel: a decode step has few tokens, and what hides a
+// load's latency there is more threads per row; a prompt has rows enough.
+int row_threads(int T) { return T <= 64 ? 1024 : 256; }
+
 unsigned flat_grid(long long n, int threads) {
     long long b = (n + threads - 1) / threads;
     if (b > 148 * 32) b = 148 * 32;
@@ -458,8 +462,8 @@ AGV_API int agv_proj_norm_store(const void* row, long long ld, const float* part
         if (smem > 48 * 1024)                                                                   \
             AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                              (int)smem));                                       \
-        agv_launch(kern, (unsigned)T, 256, smem, stream, in, (TT*)out, ldo, T, nq, nk, nv, wq,  \
-                   wk, eps, positions, cw);                                                     \
+        agv_launch(kern, (unsigned)T, row_threads(T), smem, stream, in, (TT*)out, ldo, T, nq,   \
+                   nk, nv, wq, wk, eps, positions, cw);                                         \
     } while (0)
     if (dtype == AGV_F32) AGV_PN(float);
     else if (dtype == AGV_BF16) AGV_PN(__nv_bfloat16);
@@ -501,9 +505,9 @@ AGV_API int agv_latent_prepare(const void* row, long long ld, const float* part,
         if (smem > 48 * 1024)                                                                   \
             AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                              (int)smem));                                       \
-        agv_launch(kern, (unsigned)T, 256, smem, stream, in, (TT*)out, ldo, T, q_width,         \
-                   q_latent, heads, d, r, R, G, w_q, w_c, eps, cosv, sinv, interleaved,         \
-                   positions, cw);                                                              \
+        agv_launch(kern, (unsigned)T, row_threads(T), smem, stream, in, (TT*)out, ldo, T,       \
+                   q_width, q_latent, heads, d, r, R, G, w_q, w_c, eps, cosv, sinv,             \
+                   interleaved, positions, cw);                                                 \
     } while (0)
     if (dtype == AGV_F32) AGV_LP(float);
     else if (dtype == AGV_BF16) AGV_LP(__nv_bfloat16);
