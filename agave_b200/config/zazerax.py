@@ -139,11 +139,8 @@ class ZazeraxConfig:
                                   f"design (known: {', '.join(MIXERS)})")
             m = _get(entry, "mixer", where, typ=None)
             mixer = _read_mixer(kind, m, where + "mixer.")
-            if "mlp" not in entry:
-                raise ConfigError(f"config.json: required key '{where}mlp' is missing (null: no "
-                                  "feed-forward)")
-            ff = None
-            if entry["mlp"] is not None:
+            ff = None                      # (no 'mlp' key reads as null: no feed-forward)
+            if entry.get("mlp") is not None:
                 f = entry["mlp"]
                 fk = _get(f, "kind", where + "mlp.", typ=None)
                 if fk != "dense":

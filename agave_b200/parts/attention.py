@@ -244,6 +244,10 @@ class AttentionMixer:
         view = ctx.cache.kv_view(cache_entry)
         eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
         window = s.window or 0
+        if window >= ctx.cache.max_seq_len:
+            # a window no sequence of this cache can outgrow is no window (its group keeps
+            # every key, in rows that may be fewer than the window)
+            window = 0
         n_own = nkv if self.own_kv else 0
         width = (nh + n_own) * hd + n_own * hdv
         proj = self.qkv.partial(x, cheap_sum=True)

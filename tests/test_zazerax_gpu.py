@@ -794,3 +794,14 @@ def test_trace_replay_counts_tokens_not_pages():
                                .reshape(12, V))
         rows_agree(got, torch.stack([ref[row] for ref in refs]), "float32", f"step {step}")
     shutil.rmtree(out, ignore_errors=True)
+
+
+@pytest.mark.parametrize("name, room", [("Z1", 60), ("Z2", 90), ("Z3", 64)])
+def test_a_cache_shorter_than_a_page_or_a_window(name, room):
+    """32-bit: a cache of one or two pages.  A window that still fits a sequence keeps its
+    edge although its group is no ring; a window no sequence can outgrow is none."""
+    from agave_b200.engine.api import Engine
+    folder = folder_for(name, torch.float32)
+    eng = Engine(folder, dtype="float32", max_tokens=room, ctx_size=room, max_batch=1)
+    toks = tokens(room, vocab(name), 5)
+    rows_agree(alone(eng, toks, room - 15), plain_logits(folder, toks), "float32", name)
