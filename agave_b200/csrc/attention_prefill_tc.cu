@@ -112,6 +112,9 @@ transpose_values_kernel(const __nv_bfloat16* __restrict__ v, long long kv_stride
 }
 
 // ------------------------------------------------------------------ attention
+// BIAS: the form that adds a table value to every score (a form of its own, so that the plain
+// form's softmax loop keeps its registers)
+template <bool BIAS>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const __grid_constant__ CUtensorMap map_k,
@@ -346,7 +349,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                     sv[c] = (key <= qp && key > lo) ? __uint_as_float(sr[c >> 4][c & 15]) : -INFINITY;
                 }
             }
-            if (a.dist_bias) {
+            if (BIAS) {
                 // a learned bias by distance: the last table row stands for all farther keys
                 const float* dbp = a.dist_bias + (size_t)(head0 + hl) * a.n_dist;
                 const int d0 = qp - j0;                // distance of the tile's first key
@@ -651,14 +654,22 @@ AGV_API int agv_attention_prefill_tc_ex2(const void* q, long long q_stride, cons
     const int v_stage = (hd * 128 + 1023) & ~1023;
     const size_t smem = 1024 + (size_t)a.kb * AT_M * 128 + 2 * (size_t)a.kb * AT_N * 128 +
                         2 * (size_t)v_stage + 2 * (size_t)AT_M * 128 + 256;
-    static size_t configured = 0;
-    if (smem > configured) {
-        AGV_CUDA_OK(cudaFuncSetAttribute(attention_prefill_tc_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
+    static size_t configured[2] = {0, 0};
+    const int form = dist_bias ? 1 : 0;
+    if (smem > configured[form]) {
+        if (form)
+            AGV_CUDA_OK(cudaFuncSetAttribute(attention_prefill_tc_kernel<true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        else
+            AGV_CUDA_OK(cudaFuncSetAttribute(attention_prefill_tc_kernel<false>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured[form] = smem;
     }
     dim3 grid((max_len + a.QT - 1) / a.QT, a.G > 1 ? nkv : nh, B);
-    agv_launch(attention_prefill_tc_kernel, grid, AT_THREADS, smem, stream, mq, mk, mvt, a);
+    if (form)
+        agv_launch(attention_prefill_tc_kernel<true>, grid, AT_THREADS, smem, stream, mq, mk, mvt, a);
+    else
+        agv_launch(attention_prefill_tc_kernel<false>, grid, AT_THREADS, smem, stream, mq, mk, mvt, a);
     AGV_LAUNCH_OK("attention_prefill_tc_kernel");
     return 0;
 }
